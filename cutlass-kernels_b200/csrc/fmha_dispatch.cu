@@ -1,0 +1,17 @@
+// Chooses the FMHA instantiation for (input type, P type, head dimension); the reference does this
+// with compile-time macros and a switch in main (src/fmha-pipeline/fmha_forward.cu:744-791).
+#include "fmha_launch.h"
+#include "host_util.h"
+
+namespace cfk {
+
+int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L) {
+  if (dtype == CFK_FP16 && p_dtype == CFK_FP16)
+    return head_dim == 64 ? fmha_launch_f16_f16_64(L) : fmha_launch_f16_f16_128(L);
+  if (dtype == CFK_BF16 && p_dtype == CFK_BF16)
+    return head_dim == 64 ? fmha_launch_bf16_bf16_64(L) : fmha_launch_bf16_bf16_128(L);
+  if (dtype == CFK_E4M3 && p_dtype == CFK_E4M3 && head_dim == 128) return fmha_launch_e4m3_e4m3_128(L);
+  return CFK_ERR_UNSUPPORTED;
+}
+
+}  // namespace cfk

@@ -1,0 +1,29 @@
+// Host-side launch plumbing for the FMHA kernel family: what the reference does inside
+// fmhaForwardDevice after it has built its layouts (kernel choice, shared-memory attribute, grid,
+// `iterations` back-to-back launches: src/fmha-pipeline/fmha_forward.cu:294-382).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "fmha_params.h"
+
+namespace cfk {
+
+struct FmhaLaunch {
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
+  FmhaParams p;
+  int iterations;
+  cudaStream_t stream;
+};
+
+// One function per built (input type, P type, head dim) combination; each lives in its own
+// translation unit so the combinations compile in parallel.
+int fmha_launch_f16_f16_64(const FmhaLaunch&);
+int fmha_launch_f16_f16_128(const FmhaLaunch&);
+int fmha_launch_bf16_bf16_64(const FmhaLaunch&);
+int fmha_launch_bf16_bf16_128(const FmhaLaunch&);
+int fmha_launch_e4m3_e4m3_128(const FmhaLaunch&);
+
+int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L);
+
+}  // namespace cfk

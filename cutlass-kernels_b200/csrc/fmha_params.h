@@ -1,0 +1,26 @@
+// Kernel parameter block and status codes of the FMHA kernel family (host and device).
+#pragma once
+
+namespace cfk {
+
+constexpr int kDtF16 = 0, kDtBF16 = 1, kDtE4M3 = 2;
+
+// Where a bounded wait gave up (stored in the status word).
+constexpr int kErrFmhaQFull = 101, kErrFmhaKvFull = 102, kErrFmhaKvEmpty = 103, kErrFmhaSFull = 104,
+              kErrFmhaPFull = 105, kErrFmhaOFull = 106, kErrFmhaOStaged = 107;
+
+struct FmhaParams {
+  int B, H, Sq, Skv;
+  int causal;        // key j visible to query i iff j <= i + (Skv - Sq)
+  int out_bf16;      // output element type: 0 fp16, 1 bf16
+  int nqblk;         // number of 256-row query blocks
+  int split_keys;    // bf16: CTAs whose first row sees fewer keys than this keep P as hi + lo (0 = never)
+  float scale_log2;  // softmax_scale * log2(e) * q_descale * k_descale
+  float out_scale;   // v_descale
+  float* lse;        // optional [B][H][Sq]: natural-log sum of exp of the scaled scores
+  float* mi;         // optional [B][H][Sq]: row maximum in the log2 domain
+  float* sprime;     // optional [B][H][Sq]: sum of 2^(x - mi), not inverted
+  int* status;       // device status word
+};
+
+}  // namespace cfk

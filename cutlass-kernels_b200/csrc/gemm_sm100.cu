@@ -1,0 +1,283 @@
+// Dense GEMM for sm_100a:  D[r][c] = alpha * sum_k X[r][k] * Y[c][k] + beta * D[r][c], X and Y
+// K-contiguous, D row-major with leading dimension ldd, fp32 accumulation in tensor memory.
+// It stands where the reference has gemm<> / gemm_device (src/cute-gemm-tma-gma/gemm.cu:336-463,
+// 57-334): that kernel is a single-stage TMA -> WGMMA loop that stores register accumulators straight
+// to global memory, ignores alpha / beta and accumulates in the output type.  Here:
+//
+//   warp 0     TMA producer: X (128 x 64) and Y (256 x 64) tiles into a multi-stage ring
+//   warp 1     UMMA issuer: 128 x 256 x 16 tcgen05.mma, two accumulator buffers of 256 TMEM columns
+//   warps 2-5  epilogue: TMEM -> registers -> alpha/beta -> 16-bit -> global, overlapped with the
+//              next tile's main loop
+//
+// CTAs are persistent (one per SM) and walk the tile list in bands of 8 row-tiles so that
+// concurrently running tiles share X and Y panels in L2.  The reference's column-major C
+// (gemm.cu:388-389) is the row-major D of the swapped problem (X = B, Y = A), so one kernel serves
+// both output orders.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "host_util.h"
+
+namespace cfk {
+
+constexpr int kErrGemmFull = 201, kErrGemmEmpty = 202, kErrGemmAccFull = 203, kErrGemmAccEmpty = 204;
+
+struct GemmParams {
+  int R, Cn, K, L;       // rows of X / D, rows of Y (= columns of D), reduction length, batch count
+  int64_t ldd;           // leading dimension of D (elements)
+  int64_t d_batch;       // elements between consecutive D matrices
+  void* d;
+  float alpha, beta;
+  int bf16;
+  int tiles_r, tiles_c;
+  int* status;
+};
+
+struct GemmCfg {
+  static constexpr int BM = 128, BN = 256, BK = 64;
+  static constexpr int XB = BM * BK * 2, YB = BN * BK * 2;   // bytes per stage
+  static constexpr int NSTAGE = 4;
+  static constexpr int SMEM_BYTES = 1024 + NSTAGE * (XB + YB) + 256;
+  static constexpr int NTHREADS = 192;
+  static constexpr int BAND = 8;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, int& tr, int& tc, int& batch) {
+  const int per_batch = tiles_r * tiles_c;
+  batch = tile / per_batch;
+  int t = tile - batch * per_batch;
+  const int band_tiles = GemmCfg::BAND * tiles_c;
+  const int band = t / band_tiles;
+  const int first_r = band * GemmCfg::BAND;
+  const int rows_in_band = (tiles_r - first_r) < GemmCfg::BAND ? (tiles_r - first_r) : GemmCfg::BAND;
+  t -= band * band_tiles;
+  tr = first_r + t % rows_in_band;
+  tc = t / rows_in_band;
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y, const GemmParams p) {
+  using C = GemmCfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sX = smem_base;
+  const uint32_t sY = smem_base + C::NSTAGE * C::XB;
+  const uint32_t sBar = sY + C::NSTAGE * C::YB;
+  const uint32_t bar_full = sBar;                       // [NSTAGE]
+  const uint32_t bar_empty = sBar + 8 * C::NSTAGE;      // [NSTAGE]
+  const uint32_t bar_acc_full = bar_empty + 8 * C::NSTAGE;  // [2]
+  const uint32_t bar_acc_empty = bar_acc_full + 16;         // [2]
+  uint8_t* gBar = smem_gen + (sBar - smem_base);
+  const uint32_t off_misc = 8 * (2 * C::NSTAGE + 4);
+  volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gBar + off_misc + 4);
+  const AbortCtx actx{s_abort, p.status};
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int total_tiles = p.tiles_r * p.tiles_c * p.L;
+  const int nkb = (p.K + C::BK - 1) / C::BK;
+
+  if (cta_should_skip(p.status)) return;
+  if (tid == 0) {
+    for (int i = 0; i < C::NSTAGE; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 128); }
+    *s_abort = 0u;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_y); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *s_tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int idx = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int tr, tc, b;
+        tile_coords(tile, p.tiles_r, p.tiles_c, tr, tc, b);
+        for (int kb = 0; kb < nkb; ++kb, ++idx) {
+          const int s = idx % C::NSTAGE;
+          const uint32_t ph = (idx / C::NSTAGE) & 1;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, actx, kErrGemmEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full + 8 * s, C::XB + C::YB);
+          tma_load_3d(sX + s * C::XB, &tm_x, bar_full + 8 * s, kb * C::BK, tr * C::BM, b);
+          tma_load_3d(sY + s * C::YB, &tm_y, bar_full + 8 * s, kb * C::BK, tc * C::BN, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_f16 = make_idesc(1, kFmtF16, kFmtF16, 0, 0, C::BM, C::BN);
+      constexpr uint32_t idesc_bf16 = make_idesc(1, kFmtBF16, kFmtBF16, 0, 0, C::BM, C::BN);
+      const uint32_t idesc = p.bf16 ? idesc_bf16 : idesc_f16;
+      int idx = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_ph = (local >> 1) & 1;
+        if (!mbar_wait(bar_acc_empty + 8 * buf, acc_ph ^ 1u, actx, kErrGemmAccEmpty)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + buf * 256;
+        for (int kb = 0; kb < nkb; ++kb, ++idx) {
+          const int s = idx % C::NSTAGE;
+          if (!mbar_wait(bar_full + 8 * s, (idx / C::NSTAGE) & 1, actx, kErrGemmFull)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t a0 = make_smem_desc(sX + s * C::XB, 16, 1024, kSwizzle128B);
+          const uint64_t b0 = make_smem_desc(sY + s * C::YB, 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int kk = 0; kk < C::BK / 16; ++kk)
+            umma_ss<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
+          umma_commit(bar_empty + 8 * s);
+        }
+        if (ok) umma_commit(bar_acc_full + 8 * buf);
+      }
+    }
+  } else {
+    // epilogue warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31
+    const int q = warp & 3;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const int row_in_tile = q * 32 + lane;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      int tr, tc, b;
+      tile_coords(tile, p.tiles_r, p.tiles_c, tr, tc, b);
+      const int buf = local & 1;
+      ok = mbar_wait_warp(bar_acc_full + 8 * buf, (local >> 1) & 1, actx, kErrGemmAccFull);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tr * C::BM + row_in_tile;
+      const int col0 = tc * C::BN;
+      uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+#pragma unroll 1
+      for (int c = 0; c < C::BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_x32(tmem_base + lane_base + buf * 256 + c * 32, acc);
+        tmem_wait_ld();
+        if (row < p.R) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
+            const int col = col0 + c * 32 + g * 8;
+            if (col < p.Cn) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = p.alpha * __uint_as_float(acc[g * 8 + i]);
+              uint4* dst = reinterpret_cast<uint4*>(drow + c * 32 + g * 8);
+              if (p.beta != 0.f) {
+                const uint4 old = *dst;
+                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float lo, hi;
+                  if (p.bf16) {
+                    lo = __uint_as_float(ow[i] << 16);
+                    hi = __uint_as_float(ow[i] & 0xffff0000u);
+                  } else {
+                    const __half2 h = *reinterpret_cast<const __half2*>(&ow[i]);
+                    lo = __low2float(h);
+                    hi = __high2float(h);
+                  }
+                  v[2 * i] += p.beta * lo;
+                  v[2 * i + 1] += p.beta * hi;
+                }
+              }
+              uint4 out;
+              if (p.bf16) {
+                out.x = pack_bf16x2(v[0], v[1]); out.y = pack_bf16x2(v[2], v[3]);
+                out.z = pack_bf16x2(v[4], v[5]); out.w = pack_bf16x2(v[6], v[7]);
+              } else {
+                out.x = pack_f16x2(v[0], v[1]); out.y = pack_f16x2(v[2], v[3]);
+                out.z = pack_f16x2(v[4], v[5]); out.w = pack_f16x2(v[6], v[7]);
+              }
+              *dst = out;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace cfk
+
+using namespace cfk;
+
+extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
+  if (!a || !a->a || !a->b || !a->c) return CFK_ERR_INVALID_ARG;
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->l <= 0 || a->iterations < 0) return CFK_ERR_INVALID_ARG;
+  if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16) return CFK_ERR_UNSUPPORTED;
+  if ((a->m % 8) || (a->n % 8) || (a->k % 8)) return CFK_ERR_UNSUPPORTED;
+  if (((uintptr_t)a->a | (uintptr_t)a->b | (uintptr_t)a->c) & 15u) return CFK_ERR_INVALID_ARG;
+
+  int err = CFK_OK;
+  int* status = device_status_block(&err);
+  if (!status) return err;
+
+  // Row-major C: X = A (rows m), Y = B (rows n).  Column-major C is the row-major n x m matrix of
+  // the swapped product.
+  const void* x = a->c_row_major ? a->a : a->b;
+  const void* y = a->c_row_major ? a->b : a->a;
+  const int R = a->c_row_major ? a->m : a->n;
+  const int Cn = a->c_row_major ? a->n : a->m;
+
+  CUtensorMap tm_x, tm_y;
+  const uint64_t xd[3] = {(uint64_t)a->k, (uint64_t)R, (uint64_t)a->l};
+  const uint64_t xs[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)R};
+  const uint32_t xb[3] = {GemmCfg::BK, GemmCfg::BM, 1};
+  const uint64_t yd[3] = {(uint64_t)a->k, (uint64_t)Cn, (uint64_t)a->l};
+  const uint64_t ys[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)Cn};
+  const uint32_t yb[3] = {GemmCfg::BK, GemmCfg::BN, 1};
+  int rc;
+  if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, true))) return rc;
+  if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, true))) return rc;
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.R = R; p.Cn = Cn; p.K = a->k; p.L = a->l;
+  p.ldd = Cn;
+  p.d_batch = (int64_t)R * Cn;
+  p.d = a->c;
+  p.alpha = a->alpha; p.beta = a->beta;
+  p.bf16 = a->dtype == CFK_BF16;
+  p.tiles_r = (R + GemmCfg::BM - 1) / GemmCfg::BM;
+  p.tiles_c = (Cn + GemmCfg::BN - 1) / GemmCfg::BN;
+  p.status = status;
+
+  static thread_local int attr_dev = -1;
+  static thread_local int sm_count = 0;
+  int dev = 0;
+  if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess) return CFK_ERR_NO_DRIVER;
+  if (attr_dev != dev) {
+    if (note_cuda(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg::SMEM_BYTES),
+                  "cudaFuncSetAttribute(gemm smem)") != cudaSuccess)
+      return CFK_ERR_LAUNCH;
+    if (note_cuda(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), "sm count") != cudaSuccess)
+      return CFK_ERR_LAUNCH;
+    attr_dev = dev;
+  }
+  const long long total = (long long)p.tiles_r * p.tiles_c * p.L;
+  if (total > 0x7fffffffLL) return CFK_ERR_UNSUPPORTED;
+  const int grid = (int)(total < sm_count ? total : sm_count);
+  for (int it = 0; it < a->iterations; ++it)
+    gemm_kernel<<<grid, GemmCfg::NTHREADS, GemmCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tm_x, tm_y, p);
+  return note_cuda(cudaGetLastError(), "gemm launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+}

@@ -1,0 +1,181 @@
+// Single-CTA UMMA self-test: one 128 x n x (128 bytes of K) product through each operand path the
+// FMHA and GEMM kernels rely on, so that a wrong descriptor shows up as a wrong number in a tiny
+// test and not inside a fused kernel.  No counterpart in the reference.
+#include <cstring>
+
+#include "common.cuh"
+#include "host_util.h"
+
+namespace cfk {
+
+constexpr int kErrSelfFull = 301, kErrSelfDone = 302;
+
+struct SelfParams {
+  int n;            // columns of D: 64 or 128
+  int esz;          // operand element size (1 or 2)
+  int b_mn_major;   // B stored [k][n] (1) or [n][k] (0)
+  int a_from_tmem;
+  uint32_t idesc;
+  int kind8;
+  uint32_t lbo, sbo, step;   // B descriptor fields (bytes) and start-address advance per K step
+  const uint32_t* a_words;   // A as 32-bit words, row-major [128][32], for the tensor-memory path
+  float* d;                  // [128][n]
+  int* status;
+};
+
+__global__ void __launch_bounds__(128, 1)
+selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const SelfParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA = smem_base;             // 128 rows x 128 B
+  const uint32_t sB = smem_base + 16384;     // up to 2 x (128 rows x 128 B)
+  const uint32_t sBar = sB + 32768;
+  const uint32_t bar_full = sBar, bar_done = sBar + 8;
+  volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(smem_gen + (sBar - smem_base) + 16);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(smem_gen + (sBar - smem_base) + 20);
+  const AbortCtx actx{s_abort, p.status};
+  const int tid = threadIdx.x, warp = tid >> 5;
+
+  if (cta_should_skip(p.status)) return;
+  if (tid == 0) {
+    mbar_init(bar_full, 1);
+    mbar_init(bar_done, 1);
+    *s_abort = 0u;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *s_tmem_base;
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t tD = tmem_base, tA = tmem_base + 128;
+
+  const int k_rows = 128 / p.esz;                       // K extent in elements
+  const uint32_t a_bytes = 16384;
+  const uint32_t b_bytes = p.b_mn_major ? (uint32_t)(k_rows * p.n * p.esz) : (uint32_t)(p.n * 128);
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar_full, (p.a_from_tmem ? 0u : a_bytes) + b_bytes);
+    if (!p.a_from_tmem) tma_load_3d(sA, &tm_a, bar_full, 0, 0, 0);
+    tma_load_3d(sB, &tm_b, bar_full, 0, 0, 0);
+  }
+  if (p.a_from_tmem) {
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) w[i] = p.a_words[tid * 32 + i];
+    tmem_st_x32(tA + lane_base, w);
+    tmem_wait_st();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {
+    if (mbar_wait(bar_full, 0, actx, kErrSelfFull)) {
+      tc_fence_after_sync();
+      const uint64_t a0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
+      const uint64_t b0 = make_smem_desc(sB, p.lbo, p.sbo, kSwizzle128B);
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint64_t bd = desc_advance(b0, kk * p.step);
+        if (p.a_from_tmem) {
+          if (p.kind8) umma_ts<true>(tD, tA + kk * 8, bd, p.idesc, kk > 0);
+          else umma_ts<false>(tD, tA + kk * 8, bd, p.idesc, kk > 0);
+        } else {
+          const uint64_t ad = desc_advance(a0, kk * 32);
+          if (p.kind8) umma_ss<true>(tD, ad, bd, p.idesc, kk > 0);
+          else umma_ss<false>(tD, ad, bd, p.idesc, kk > 0);
+        }
+      }
+      umma_commit(bar_done);
+    }
+  }
+  if (mbar_wait_warp(bar_done, 0, actx, kErrSelfDone)) {
+    tc_fence_after_sync();
+    for (int c = 0; c < p.n / 32; ++c) {
+      uint32_t acc[32];
+      tmem_ld_x32(tD + lane_base + c * 32, acc);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) p.d[(size_t)tid * p.n + c * 32 + i] = __uint_as_float(acc[i]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+}  // namespace cfk
+
+using namespace cfk;
+
+extern "C" int cfk_selftest_umma(const void* a, const void* b, float* d, int n, int a_fmt, int b_fmt, int b_mn_major,
+                                 int a_from_tmem, int lbo, int sbo, int step, cfk_stream_t stream) {
+  if (!a || !b || !d) return CFK_ERR_INVALID_ARG;
+  if (n != 64 && n != 128) return CFK_ERR_UNSUPPORTED;
+  if (a_fmt < CFK_FP16 || a_fmt > CFK_E4M3 || b_fmt < CFK_FP16 || b_fmt > CFK_E4M3) return CFK_ERR_INVALID_ARG;
+  const int esz = dtype_size(a_fmt);
+  if (dtype_size(b_fmt) != esz) return CFK_ERR_UNSUPPORTED;
+  if (b_mn_major && n * esz < 128) return CFK_ERR_UNSUPPORTED;
+  int err = CFK_OK;
+  int* status = device_status_block(&err);
+  if (!status) return err;
+
+  const int k = 128 / esz;
+  CUtensorMap tm_a, tm_b;
+  {
+    const uint64_t dims[3] = {(uint64_t)k, 128, 1};
+    const uint64_t str[2] = {128, 128 * 128};
+    const uint32_t box[3] = {(uint32_t)k, 128, 1};
+    int rc = encode_tiled(&tm_a, a_fmt, 3, a, dims, str, box, true);
+    if (rc) return rc;
+  }
+  if (!b_mn_major) {
+    const uint64_t dims[3] = {(uint64_t)k, (uint64_t)n, 1};
+    const uint64_t str[2] = {128, (uint64_t)128 * n};
+    const uint32_t box[3] = {(uint32_t)k, (uint32_t)n, 1};
+    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, true);
+    if (rc) return rc;
+  } else {
+    const uint64_t span = 128 / esz;                 // elements per 128-byte span of n
+    const uint64_t nspan = (uint64_t)n / span;
+    const uint64_t dims[3] = {span, (uint64_t)k, nspan};
+    const uint64_t str[2] = {(uint64_t)n * esz, 128};
+    const uint32_t box[3] = {(uint32_t)span, (uint32_t)k, (uint32_t)nspan};
+    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, true);
+    if (rc) return rc;
+  }
+  SelfParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.n = n; p.esz = esz; p.b_mn_major = b_mn_major; p.a_from_tmem = a_from_tmem;
+  p.kind8 = esz == 1;
+  const uint32_t af = a_fmt == CFK_BF16 ? kFmtBF16 : 0u, bf = b_fmt == CFK_BF16 ? kFmtBF16 : 0u;
+  p.idesc = make_idesc(1, af, bf, 0, b_mn_major ? 1 : 0, 128, (uint32_t)n);
+  // defaults: K-major B -> 8-row groups 1024 B apart, 32 B per K step; MN-major B -> column groups
+  // one [k rows][128 B] block apart, 8-row groups 1024 B apart, (32/esz) rows per K step.
+  p.lbo = b_mn_major ? (uint32_t)(k * 128) : 16u;
+  p.sbo = 1024u;
+  p.step = b_mn_major ? (uint32_t)((32 / esz) * 128) : 32u;
+  if (lbo >= 0) p.lbo = (uint32_t)lbo;
+  if (sbo >= 0) p.sbo = (uint32_t)sbo;
+  if (step >= 0) p.step = (uint32_t)step;
+  p.a_words = reinterpret_cast<const uint32_t*>(a);
+  p.d = d;
+  p.status = status;
+  const int smem = 1024 + 16384 + 32768 + 64;
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess) return CFK_ERR_NO_DRIVER;
+  if (attr_dev != dev) {
+    if (note_cuda(cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                  "cudaFuncSetAttribute(selftest smem)") != cudaSuccess)
+      return CFK_ERR_LAUNCH;
+    attr_dev = dev;
+  }
+  selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(tm_a, tm_b, p);
+  return note_cuda(cudaGetLastError(), "selftest launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+}

@@ -1,0 +1,143 @@
+/*
+ * cfk_b200.h — C ABI of libcfk_b200.so (sm_100a flash-attention forward + GEMM).
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status (0 = success) and
+ * never throws, exits or synchronises the device unless its comment says so.  Buffers belong to
+ * the caller; the library allocates one 256-byte status block per device on first use and
+ * nothing else.  Kernels are enqueued on the stream that is passed in.
+ *
+ * The reference project has no FFI: its "API" is the templated host launchers inside each
+ * program.  Each function below names the launcher it replaces (paths inside the reference).
+ */
+#ifndef CFK_B200_H_
+#define CFK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* cfk_stream_t; /* == cudaStream_t */
+
+enum cfk_dtype { CFK_FP16 = 0, CFK_BF16 = 1, CFK_E4M3 = 2, CFK_FP32 = 3 };
+
+enum cfk_status {
+  CFK_OK = 0,
+  CFK_ERR_INVALID_ARG = 1,   /* null pointer, non-positive size, misaligned pointer or stride */
+  CFK_ERR_UNSUPPORTED = 2,   /* a shape / type combination no kernel was built for */
+  CFK_ERR_DESCRIPTOR = 3,    /* the driver refused a TMA descriptor */
+  CFK_ERR_LAUNCH = 4,        /* cudaFuncSetAttribute / launch failed; see cfk_last_cuda_error */
+  CFK_ERR_NO_DRIVER = 5,     /* no CUDA driver / device */
+  CFK_ERR_DEVICE_WAIT = 6    /* a bounded wait inside a kernel gave up; see cfk_device_status */
+};
+
+/*
+ * Flash-attention forward:  O = softmax(Q K^T * softmax_scale [causal mask]) V.
+ *
+ * Replaces fmhaForwardDevice<PrecType,Gemm2Type,SoftType,OutputType,HEADDIM>(SEQLEN, KEYLEN,
+ * NUMHEADS, BATCH, Q, K, V, S, O, miOut, sPrimeOut, iterations, scale, stream)
+ * (src/fmha-pipeline/fmha_forward.cu:86-93) and the legacy fmhaForwardDevice<PrecType,AccumType,
+ * HEADDIM> (src/fmha/fmha_forward.cu:425-430).  Differences a caller must know:
+ *   - softmax_scale is the plain factor (e.g. 1/sqrt(D)); the reference passes it pre-multiplied
+ *     by log2(e) (src/fmha-pipeline/fmha_forward.cu:452-454).  include/cfk_compat.hpp converts.
+ *   - the S x S debug matrix of the reference (argument S) is not produced.
+ *   - additions: causal flag, bf16, log-sum-exp output, per-tensor e4m3 de-scale factors,
+ *     explicit strides.  Mixed operand formats in one MMA (fp16 P with bf16 V) are not possible:
+ *     the hardware rejects them as an illegal instruction.
+ * Tensors are [batch][seq][head][head_dim] with head_dim contiguous (the reference's layout,
+ * fmha_forward.cu:151-152).  A stride of 0 means "packed".  Strides are in elements; every
+ * stride times the element size must be a multiple of 16 bytes and every base pointer 16-byte
+ * aligned.  head_dim must be 64 or 128 (128 only for e4m3).  Accumulation and softmax are fp32.
+ */
+typedef struct cfk_fmha_args {
+  int dtype;      /* cfk_dtype of Q, K and V: FP16, BF16 or E4M3 */
+  int out_dtype;  /* cfk_dtype of O: FP16 or BF16 */
+  int p_split_keys; /* P (unnormalised probabilities) is rounded to the input type before P*V, as the
+                       reference does (fmha_consumer.h:54).  bf16 only: 256-row query blocks whose first
+                       row sees fewer keys than this keep P as a two-term bf16 sum (hi + lo, two MMAs),
+                       because with few keys bf16's 8-bit rounding of P is not averaged out.
+                       -1 = default (1024), 0 = never.  Ignored for fp16 / e4m3. */
+  int batch, heads, seqlen_q, seqlen_kv, head_dim;
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;     /* optional, [batch][heads][seqlen_q]: ln(sum_j exp(scale * q.k_j)) */
+  float* mi;      /* optional, reference's miOut: row maximum in the log2 domain */
+  float* sprime;  /* optional, reference's sPrimeOut: sum_j 2^(x_j - mi), not inverted */
+  int64_t q_stride[3]; /* batch, seq, head (elements); all 0 = packed */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  float softmax_scale;
+  int causal;     /* key j visible to query i iff j <= i + (seqlen_kv - seqlen_q) */
+  float q_descale, k_descale, v_descale; /* multiply the stored values to get real ones; use 1 for 16-bit */
+  int iterations; /* number of back-to-back launches (the reference's loop, fmha_forward.cu:375-382) */
+} cfk_fmha_args;
+
+int cfk_fmha_forward(const cfk_fmha_args* args, cfk_stream_t stream);
+
+/*
+ * GEMM:  C[m,n] = alpha * sum_k A[m,k] * B[n,k] + beta * C[m,n], fp32 accumulation, batched over L.
+ *
+ * Replaces gemm<TA,TB,TC,Alpha,Beta>(m, n, k, alpha, A, ldA, B, ldB, beta, C, ldC, A_out, B_out,
+ * L, stream) (src/cute-gemm-tma-gma/gemm.cu:336-339).  A is M x K row-major, B is N x K row-major
+ * (i.e. column-major K x N), both K-contiguous, as the reference builds them (gemm.cu:366-379); C is
+ * column-major with leading dimension M by default (gemm.cu:388-389) or row-major with leading
+ * dimension N.  Unlike the reference, alpha and beta are honoured and the accumulator is fp32.
+ * K must be a multiple of 8 and M, N multiples of 8; pointers 16-byte aligned.
+ */
+typedef struct cfk_gemm_args {
+  int dtype;      /* FP16 or BF16 for A, B and C */
+  int m, n, k, l;
+  const void* a;
+  const void* b;
+  void* c;
+  float alpha, beta;
+  int c_row_major; /* 0: column-major (reference), 1: row-major */
+  int iterations;
+} cfk_gemm_args;
+
+int cfk_gemm(const cfk_gemm_args* args, cfk_stream_t stream);
+
+/*
+ * Device-side random fills, element i depends only on (seed, first_index + i).
+ * Replaces cfk::initialize_rand / initialize_const (include/utils/random.hpp:20-50).
+ * kind 0: N(0,1); kind 1: U[-1,1]; kind 2: constant `value`.  The result is value * scale
+ * rounded to `dtype`.
+ */
+int cfk_fill(void* dst, int dtype, int64_t n, uint64_t seed, int64_t first_index, int kind, float scale,
+             float value, cfk_stream_t stream);
+
+/* Element-wise conversion on the device between FP32 and any cfk_dtype (either side may be FP32). */
+int cfk_convert(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n, float scale,
+                cfk_stream_t stream);
+
+/*
+ * Reads (and clears) the status word of the current device.  Synchronises the device.
+ * 0 = no kernel wait gave up; otherwise the code tells which wait did (1xx FMHA, 2xx GEMM).
+ */
+int cfk_device_status(int* code_out);
+
+/* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
+const char* cfk_last_cuda_error(void);
+
+/* Library version, e.g. 100 = 0.1.0. */
+int cfk_version(void);
+
+/*
+ * Single-CTA UMMA self-test used by the GPU test-suite to prove each operand-descriptor form
+ * (K-major / MN-major shared-memory operands, A from tensor memory, 16-bit and e4m3 kinds) against
+ * a CPU product.  D[128][n] (fp32, row-major) = A[128][k] * B, where B is [n][k] (b_mn_major = 0)
+ * or [k][n] (b_mn_major = 1).  k * elem_size must be 128; n is 64 or 128.  a_from_tmem routes A
+ * through tensor memory.  a_fmt / b_fmt are cfk_dtype codes.  lbo / sbo / step override the
+ * descriptor fields of B when non-negative.  No counterpart in the reference.
+ */
+int cfk_selftest_umma(const void* a, const void* b, float* d, int n, int a_fmt, int b_fmt, int b_mn_major,
+                      int a_from_tmem, int lbo, int sbo, int step, cfk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CFK_B200_H_ */
