@@ -60,6 +60,11 @@ struct FmhaCfg {
   static constexpr uint32_t IDESC_QK = make_idesc(1, FMT_IN, FMT_IN, 0, 0, BM, BN);
   static constexpr uint32_t IDESC_PV = make_idesc(1, FMT_P, FMT_IN, 0, 1, BM, HD);
   static constexpr int NTHREADS = 384;
+  // Register budget after setmaxnreg.  The pool is what the CTA was launched with: 384 threads at the
+  // 168 registers a 384-thread launch bound allows.  setmaxnreg.inc blocks until the registers it asks
+  // for are free, with no time limit, so the sum below must never exceed that pool.
+  static constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 216, AUX_REGS = 72;
+  static_assert(2 * 128 * SOFTMAX_REGS + 128 * AUX_REGS <= NTHREADS * LAUNCH_REGS, "setmaxnreg would block forever");
   // log2-domain slack before the running maximum is moved, and a constant exponent offset that puts
   // P into the well-represented range of its type (it cancels in O / l).
   static constexpr float TAU = (PT == kDtE4M3) ? 2.0f : 8.0f;
@@ -164,7 +169,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp >= 8) {
    // Third warpgroup: hands most of its registers to the softmax warpgroups.
-   setmaxnreg_dec<64>();
+   setmaxnreg_dec<C::AUX_REGS>();
    if (warp == 9) {
     // =========================== TMA producer ===========================
     if (lane == 0 && n_kv > 0) {
@@ -260,7 +265,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
    }
   } else {
     // =========================== softmax + epilogue ===========================
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<C::SOFTMAX_REGS>();
     const int t = warp >> 2;               // query tile of this warpgroup
     const int r = tid & 127;               // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;

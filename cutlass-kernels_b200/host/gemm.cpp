@@ -1,0 +1,128 @@
+// gemm — command-line driver shaped like the reference's CuTe GEMM program
+// (src/cute-gemm-tma-gma/gemm.cu:656-691: positional `type m n k l`, type 3 = half; :469-654: random
+// inputs in [-1,1], timing over many iterations, GFLOP/s = 2*m*n*k*l / time, element-wise comparison).
+// The reference compares bit-exactly against cuBLAS; this driver has no BLAS to lean on, so it checks a
+// sample of entries against a float64 dot product of the same operands, to fp16 output rounding.
+//
+//   gemm [type=3] [m=5120] [n=5120] [k=4096] [l=1] [iterations=100] [alpha=1] [beta=0]
+//   type 3 = fp16, type 4 = bf16 (addition).  Types 1/2 of the reference (fp32 as tf32, fp64) are not built.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "cfk_compat.hpp"
+
+#define CUDA_OK(x)                                                                         \
+  do {                                                                                     \
+    cudaError_t e_ = (x);                                                                  \
+    if (e_ != cudaSuccess) {                                                               \
+      std::fprintf(stderr, "%s failed: %s\n", #x, cudaGetErrorString(e_));                 \
+      return 1;                                                                            \
+    }                                                                                      \
+  } while (0)
+
+template <typename T>
+static int run(int dtype, int m, int n, int k, int l, int iterations, float alpha, float beta) {
+  std::printf("M = %d\nN = %d\nK = %d\nL = %d\n", m, n, k, l);
+  const size_t na = (size_t)l * m * k, nb = (size_t)l * n * k, nc = (size_t)l * m * n;
+  T *a, *b, *c;
+  CUDA_OK(cudaMalloc(&a, na * sizeof(T)));
+  CUDA_OK(cudaMalloc(&b, nb * sizeof(T)));
+  CUDA_OK(cudaMalloc(&c, nc * sizeof(T)));
+  if (cfk_fill(a, dtype, (int64_t)na, 1, 0, 1, 1.f, 0.f, nullptr)) return 1;   // U[-1,1], gemm.cu:482-485
+  if (cfk_fill(b, dtype, (int64_t)nb, 2, 0, 1, 1.f, 0.f, nullptr)) return 1;
+  if (cfk_fill(c, dtype, (int64_t)nc, 3, 0, 1, 1.f, 0.f, nullptr)) return 1;
+
+  std::vector<float> hc0;
+  float* tmp = nullptr;
+  const size_t sample_c = (size_t)m * n;   // first batch entry
+  CUDA_OK(cudaMalloc(&tmp, sample_c * sizeof(float)));
+  if (beta != 0.f) {
+    hc0.resize(sample_c);
+    if (cfk_convert(c, dtype, tmp, CFK_FP32, (int64_t)sample_c, 1.f, nullptr)) return 1;
+    CUDA_OK(cudaMemcpy(hc0.data(), tmp, sample_c * sizeof(float), cudaMemcpyDeviceToHost));
+  }
+
+  gemm(m, n, k, alpha, a, k, b, k, beta, c, m, (T*)nullptr, (T*)nullptr, l, 0);
+  CUDA_OK(cudaDeviceSynchronize());
+  if (cfk::last_status() != CFK_OK) return 1;
+
+  // check a sample of entries of batch 0 (column-major C: element (i, j) at j*m + i)
+  std::vector<float> hc(sample_c);
+  if (cfk_convert(c, dtype, tmp, CFK_FP32, (int64_t)sample_c, 1.f, nullptr)) return 1;
+  CUDA_OK(cudaMemcpy(hc.data(), tmp, sample_c * sizeof(float), cudaMemcpyDeviceToHost));
+  std::vector<float> ha((size_t)m * k), hb((size_t)n * k);
+  float* tmp2;
+  CUDA_OK(cudaMalloc(&tmp2, (ha.size() > hb.size() ? ha.size() : hb.size()) * sizeof(float)));
+  if (cfk_convert(a, dtype, tmp2, CFK_FP32, (int64_t)ha.size(), 1.f, nullptr)) return 1;
+  CUDA_OK(cudaMemcpy(ha.data(), tmp2, ha.size() * sizeof(float), cudaMemcpyDeviceToHost));
+  if (cfk_convert(b, dtype, tmp2, CFK_FP32, (int64_t)hb.size(), 1.f, nullptr)) return 1;
+  CUDA_OK(cudaMemcpy(hb.data(), tmp2, hb.size() * sizeof(float), cudaMemcpyDeviceToHost));
+  cudaFree(tmp2);
+  cudaFree(tmp);
+  const double ulp = dtype == CFK_FP16 ? std::ldexp(1.0, -10) : std::ldexp(1.0, -7);
+  int failures = 0;
+  unsigned long long s = 12345;
+  for (int t = 0; t < 4096; ++t) {
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    const int i = (int)((s >> 33) % (unsigned)m);
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    const int j = (int)((s >> 33) % (unsigned)n);
+    double acc = 0;
+    for (int kk = 0; kk < k; ++kk) acc += (double)ha[(size_t)i * k + kk] * hb[(size_t)j * k + kk];
+    double want = alpha * acc;
+    if (beta != 0.f) want += (double)beta * hc0[(size_t)j * m + i];
+    const double got = hc[(size_t)j * m + i];
+    if (std::fabs(got - want) > ulp * std::fmax(1.0, std::fabs(want)) + 1e-3) {
+      if (failures < 5) std::printf("C[%d,%d]: got %g want %g\n", i, j, got, want);
+      ++failures;
+    }
+  }
+  std::printf("sampled check: %s (%d of 4096 entries differ)\n", failures ? "failed" : "passed", failures);
+
+  // timing: `iterations` back-to-back launches between two events (gemm.cu:592-601 uses 1000)
+  cudaEvent_t e0, e1;
+  CUDA_OK(cudaEventCreate(&e0));
+  CUDA_OK(cudaEventCreate(&e1));
+  cfk_gemm_args g{};
+  g.dtype = dtype; g.m = m; g.n = n; g.k = k; g.l = l; g.a = a; g.b = b; g.c = c;
+  g.alpha = alpha; g.beta = 0.f; g.c_row_major = 0; g.iterations = 5;
+  if (cfk_gemm(&g, nullptr)) return 1;
+  CUDA_OK(cudaDeviceSynchronize());
+  g.iterations = iterations;
+  CUDA_OK(cudaEventRecord(e0, 0));
+  if (cfk_gemm(&g, nullptr)) return 1;
+  CUDA_OK(cudaEventRecord(e1, 0));
+  CUDA_OK(cudaDeviceSynchronize());
+  float ms_total = 0.f;
+  CUDA_OK(cudaEventElapsedTime(&ms_total, e0, e1));
+  int code = 0;
+  if (cfk_device_status(&code) != CFK_OK) { std::printf("device status word %d\n", code); return 1; }
+  const double ms = ms_total / (iterations > 0 ? iterations : 1);
+  const double gflops = 2.0 * m * n * (double)k * l * 1e-9;
+  std::printf("CUTE_GEMM:     [%6.1f]GFlop/s  (%6.4f)ms\n", gflops / (ms * 1e-3), ms);
+  cudaFree(a); cudaFree(b); cudaFree(c);
+  return failures ? 2 : 0;
+}
+
+int main(int argc, char** argv) {
+  int type = 3, m = 5120, n = 5120, k = 4096, l = 1, iterations = 100;   // defaults: gemm.cu:661-675
+  float alpha = 1.f, beta = 0.f;
+  if (argc > 1) type = std::atoi(argv[1]);
+  if (argc > 2) m = std::atoi(argv[2]);
+  if (argc > 3) n = std::atoi(argv[3]);
+  if (argc > 4) k = std::atoi(argv[4]);
+  if (argc > 5) l = std::atoi(argv[5]);
+  if (argc > 6) iterations = std::atoi(argv[6]);
+  if (argc > 7) alpha = (float)std::atof(argv[7]);
+  if (argc > 8) beta = (float)std::atof(argv[8]);
+  if (type == 3) return run<__half>(CFK_FP16, m, n, k, l, iterations, alpha, beta);
+  if (type == 4) return run<__nv_bfloat16>(CFK_BF16, m, n, k, l, iterations, alpha, beta);
+  std::printf("type %d is not built (3 = fp16, 4 = bf16)\n", type);
+  return 1;
+}

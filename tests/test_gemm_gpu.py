@@ -1,0 +1,65 @@
+"""GEMM through the C ABI against the CPU oracle (fp32 accumulation of the same 16-bit operands)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import TORCH_DT
+
+pytestmark = pytest.mark.gpu
+
+
+def run(lib, oracle, M, N, K, dtype=0, row_major=False, alpha=1.0, beta=0.0, L=1, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    dt = TORCH_DT[dtype]
+    a = (torch.rand(L, M, K, generator=g) * 2 - 1).to(dt)
+    b = (torch.rand(L, N, K, generator=g) * 2 - 1).to(dt)
+    c0 = (torch.rand(L, M, N, generator=g) * 2 - 1).to(dt)
+    c_store = (c0 if row_major else c0.transpose(1, 2)).contiguous().cuda()
+    lib.gemm(a.cuda(), b.cuda(), c_store, dtype=dtype, m=M, n=N, k=K, l=L, alpha=alpha, beta=beta,
+             c_row_major=row_major)
+    lib.check_device()
+    got = c_store.float().cpu()
+    got = got if row_major else got.transpose(1, 2)
+    for l in range(L):
+        ref = oracle.gemm(a[l].float().numpy(), b[l].float().numpy(), alpha=alpha, beta=beta,
+                          c_in=c0[l].float().numpy() if beta else None)
+        # output rounding to the 16-bit type: half an ulp of the result, plus fp32 summation-order noise
+        ulp = 2.0 ** (-10 if dtype == 0 else -7)
+        tol = ulp * np.maximum(np.abs(ref), 1.0) + 1e-4
+        err = np.abs(got[l].numpy() - ref)
+        assert (err <= tol).all(), (err.max(), np.abs(ref).max())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (1024, 1024, 1024), (2048, 768, 4096)])
+@pytest.mark.parametrize("row_major", [False, True])
+def test_gemm_matches_oracle(lib, oracle, cuda, M, N, K, row_major):
+    run(lib, oracle, M, N, K, row_major=row_major)
+
+
+def test_gemm_alpha_beta_bf16_ragged(lib, oracle, cuda):
+    run(lib, oracle, 1000, 776, 264, dtype=1, alpha=0.5, beta=2.0)
+    run(lib, oracle, 1000, 776, 264, dtype=0, alpha=-1.25, beta=0.5, row_major=True)
+
+
+def test_gemm_batched(lib, oracle, cuda):
+    run(lib, oracle, 384, 512, 320, L=3)
+
+
+def test_gemm_linearity_at_full_size(lib, cuda):
+    """8192^3 (the baseline's GEMM config): C(alpha=2) == 2 * C(alpha=1) exactly in fp16 (power-of-two
+    scaling commutes with rounding while nothing overflows), and a sampled set of entries equals an
+    fp64 dot product of the same operands to fp16 rounding."""
+    n = 8192
+    torch.manual_seed(1)
+    a = (torch.rand(n, n, device="cuda") * 2 - 1).half()
+    b = (torch.rand(n, n, device="cuda") * 2 - 1).half()
+    c1 = torch.empty(n, n, device="cuda", dtype=torch.float16)
+    c2 = torch.empty_like(c1)
+    lib.gemm(a, b, c1, dtype=0, m=n, n=n, k=n)
+    lib.gemm(a, b, c2, dtype=0, m=n, n=n, k=n, alpha=2.0)
+    lib.check_device()
+    assert torch.equal(c2, c1 * 2)
+    idx = torch.randint(0, n, (64, 2))
+    for m, nn in idx.tolist():
+        ref = float(a[m].double() @ b[nn].double())
+        assert abs(float(c1[nn, m]) - ref) <= 2.0 ** -10 * max(1.0, abs(ref)) + 2e-3   # column-major C
