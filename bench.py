@@ -64,7 +64,7 @@ class ClockSampler:
             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -207,7 +207,7 @@ def run_reference(args, wl, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
@@ -349,7 +349,7 @@ def main():
         worst["slices_checked"] = len(sl)
         line["parity"] = worst
         # CPU baseline: the oracle on whole slices of the same workload, ~15 s
-        n_try = 16
+        n_try = B * H
         cpu_sl = slices_for_cpu(torch, wl, q, k, v, scales, n_try)
         done, t_cpu, cpu_tf = cpu_attention_sample(orc, torch, wl, cpu_sl, budget_s=12.0)
         line["cpu_baseline"] = {"value": cpu_tf, "unit": "TFLOP/s", "cores": orc.threads, "kind": "port",

@@ -21,7 +21,9 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
                 6: "DEVICE_WAIT"}
 
 EXPORTS = ["cfk_fmha_forward", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
-           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma"]
+           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_set_tunable", "cfk_get_tunable"]
+
+TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB = 0, 1
 
 
 class FmhaArgs(C.Structure):
@@ -149,6 +151,14 @@ class CfkLib:
 
     def last_error(self) -> str:
         return (self.lib.cfk_last_cuda_error() or b"").decode()
+
+    def set_tunable(self, which: int, value: int) -> None:
+        rc = int(self.lib.cfk_set_tunable(which, value))
+        if rc:
+            raise CfkError(rc, "cfk_set_tunable")
+
+    def get_tunable(self, which: int) -> int:
+        return int(self.lib.cfk_get_tunable(which))
 
     def version(self) -> int:
         return int(self.lib.cfk_version())

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <mutex>
@@ -154,6 +155,11 @@ __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, int
     store_as(dst, ddt, i, load_as(src, sdt, i) * scale);
 }
 
+// Tunables (process-wide).  Defaults are the measured best on B200.
+// EXP_EMU -1 = by type: 1 of 4 pairs for 16-bit inputs, 2 of 4 for e4m3 (measured best on B200).
+static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 256};
+static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {256}};
+
 static bool valid_dtype(int dt) { return dt >= CFK_FP16 && dt <= CFK_FP32; }
 
 }  // namespace cfk
@@ -161,6 +167,20 @@ static bool valid_dtype(int dt) { return dt >= CFK_FP16 && dt <= CFK_FP32; }
 using namespace cfk;
 
 extern "C" int cfk_version(void) { return 100; }
+
+extern "C" int cfk_set_tunable(int which, int value) {
+  if (which < 0 || which >= CFK_TUNE_COUNT) return CFK_ERR_INVALID_ARG;
+  if (value < 0) value = kTunableDefault[which];
+  if (which == CFK_TUNE_FMHA_EXP_EMU && value > 3) return CFK_ERR_INVALID_ARG;
+  if (which == CFK_TUNE_FMHA_GROUP_MB && (value < 1 || value > 1024)) return CFK_ERR_INVALID_ARG;
+  g_tunable[which].store(value);
+  return CFK_OK;
+}
+
+extern "C" int cfk_get_tunable(int which) {
+  if (which < 0 || which >= CFK_TUNE_COUNT) return -1;
+  return g_tunable[which].load();
+}
 
 extern "C" const char* cfk_last_cuda_error(void) { return g_last_error.c_str(); }
 
@@ -269,6 +289,32 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   p.lse = a->lse; p.mi = a->mi; p.sprime = a->sprime;
   p.status = status;
   L.iterations = a->iterations;
+  L.exp_emu = g_tunable[CFK_TUNE_FMHA_EXP_EMU].load();
+  if (L.exp_emu < 0) L.exp_emu = a->dtype == CFK_E4M3 ? 2 : 1;
+  {
+    // Causal: CTAs differ in length, so heads are interleaved (heaviest blocks of a group of heads first);
+    // the group is sized so that its K and V stay in L2.  Non-causal: one head at a time.
+    const long long kv_bytes = 2LL * a->seqlen_kv * a->head_dim * esz;
+    long long grp = a->causal ? ((long long)g_tunable[CFK_TUNE_FMHA_GROUP_MB].load() << 20) / kv_bytes : 1;
+    const long long bh = (long long)a->batch * a->heads;
+    p.group = (int)(grp < 1 ? 1 : (grp > bh ? bh : grp));
+  }
+  if ((long long)p.nqblk * a->heads * a->batch > 0x7fffffffLL) return CFK_ERR_UNSUPPORTED;
   L.stream = (cudaStream_t)stream;
   return fmha_dispatch(a->dtype, pdt, a->head_dim, L);
 }
+
+#ifdef CFK_FMHA_PROFILE
+// Profiling builds only: copies the 64-word status block (per-role cycle counters live in words 8..)
+// to the host and clears it.
+extern "C" int cfk_debug_read_status_block(int* out64) {
+  int err = CFK_OK;
+  int* blk = device_status_block(&err);
+  if (!blk) return err;
+  if (note_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize") != cudaSuccess) return CFK_ERR_LAUNCH;
+  if (note_cuda(cudaMemcpy(out64, blk, 256, cudaMemcpyDeviceToHost), "cudaMemcpy(status block)") != cudaSuccess)
+    return CFK_ERR_LAUNCH;
+  (void)note_cuda(cudaMemset(blk, 0, 256), "cudaMemset(status block)");
+  return CFK_OK;
+}
+#endif

@@ -22,6 +22,8 @@
 // (online_softmax.h:144-165).  Both carry the same factor into O and the row sum, so O / l is
 // unchanged.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 #include "fmha_params.h"
 
@@ -71,7 +73,41 @@ struct FmhaCfg {
   static constexpr float PSHIFT = (PT == kDtE4M3) ? 6.0f : 0.0f;
 };
 
-template <int DT, int PT, int HD>
+// exp2 of a pair of log2-domain scores on the special-function unit ...
+__device__ __forceinline__ float2 exp2_pair_sfu(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
+// ... or on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic whose relative
+// error (7.5e-5) is below the rounding step of every P format; 2^n by adding n to the exponent bits.
+// The special-function unit delivers 16 results per clock per SM, exactly what the tensor core consumes
+// at D=128, so a share of the exponentials is moved here (packed two-wide FMA instructions).
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));      // 1.5 * 2^23: n sits in the low bits
+  const float2 nf = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
+  float2 q = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+  q = __ffma2_rn(q, f, make_float2(0.6932609677f, 0.6932609677f));
+  q = __ffma2_rn(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return q;
+}
+
+// Optional per-role cycle counters (build with -DCFK_FMHA_PROFILE): lane 0 of the first warp of softmax
+// warpgroup 0 and the UMMA thread add the cycles they spend in each phase to words 8.. of the status
+// block.  Off in the shipped library.
+#ifdef CFK_FMHA_PROFILE
+#define CFK_PROF_DECL(n) long long prof_t[n] = {0}; long long prof_last = clock64();
+#define CFK_PROF_MARK(i) { const long long now_ = clock64(); prof_t[i] += now_ - prof_last; prof_last = now_; }
+#define CFK_PROF_FLUSH(base, n, cond) if (cond) { for (int i_ = 0; i_ < n; ++i_) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + base + i_, (unsigned long long)prof_t[i_]); }
+#else
+#define CFK_PROF_DECL(n)
+#define CFK_PROF_MARK(i)
+#define CFK_PROF_FLUSH(base, n, cond)
+#endif
+
+// EMU: of every four pairs of probabilities, how many are computed on the FMA pipe (0..3).
+template <int DT, int PT, int HD, int EMU>
 __global__ void __launch_bounds__(384, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -103,10 +139,22 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
 
-  // Work item.  Heavier (later) query blocks first when causal, so the tail of the grid is light.
-  const int qblk = p.causal ? (p.nqblk - 1 - (int)blockIdx.x) : (int)blockIdx.x;
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
+  // Work item.  The grid is one-dimensional.  (batch, head) pairs are taken in groups whose K and V
+  // fit in L2 together; inside a group the 256-row query blocks go from the last (heaviest when causal)
+  // to the first, all pairs of the group side by side, so that CTAs finish together and the tail is light.
+  int qblk, head, batch;
+  {
+    const int bh_total = p.B * p.H;
+    const int per_group = p.group * p.nqblk;
+    const int g = (int)blockIdx.x / per_group;
+    const int r = (int)blockIdx.x - g * per_group;
+    const int left = bh_total - g * p.group;
+    const int gsz = left < p.group ? left : p.group;
+    qblk = p.nqblk - 1 - r / gsz;
+    const int bh = g * p.group + r % gsz;
+    batch = bh / p.H;
+    head = bh - batch * p.H;
+  }
   const int nkv_total = (p.Skv + C::BN - 1) / C::BN;
   const int diag_off = p.Skv - p.Sq;
   auto tiles_for = [&](int t) -> int {
@@ -221,8 +269,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       };
 
+      CFK_PROF_DECL(4)
       ok = mbar_wait(bar_q_full, 0, actx, kErrFmhaQFull);
       if (ok) ok = mbar_wait(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
+      CFK_PROF_MARK(0)
       if (ok) {
         tc_fence_after_sync();
         for (int t = 0; t < 2; ++t)
@@ -235,11 +285,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int j = 0; j < n_kv && ok; ++j) {
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
+        CFK_PROF_MARK(3)
         ok = mbar_wait(bar_kv_full + 8 * vslot, (vidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+        CFK_PROF_MARK(1)
         bool k_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_of(t)) continue;
+          CFK_PROF_MARK(3)
           ok = mbar_wait(bar_p_full + 8 * t, j & 1, actx, kErrFmhaPFull);
+          CFK_PROF_MARK(2)
           if (!ok) break;
           tc_fence_after_sync();
           issue_pv(t, vslot, j > 0 ? 1u : 0u);
@@ -261,6 +315,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (j + 1 < n_kv) umma_commit(bar_kv_empty + 8 * kslot);
         }
       }
+      CFK_PROF_MARK(3)
+      CFK_PROF_FLUSH(8, 4, true)
     }
    }
   } else {
@@ -273,6 +329,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tO = tmem_base + lane_base + C::O_COL0 + t * HD;
     const int row_g = qblk * 256 + t * 128 + r;     // global query row
     const int n_my = n_of(t);
+    // smallest last-visible-key index over the rows of this tile
+    const int tile_min_lim = p.causal ? min(p.Skv - 1, qblk * 256 + t * 128 + diag_off) : p.Skv - 1;
     const float sl = p.scale_log2;
 
     float m_ref = 0.f;       // maximum in use (raw score units)
@@ -281,8 +339,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     uint32_t sreg[128];
 
+    CFK_PROF_DECL(8)
     for (int j = 0; j < n_my; ++j) {
+      CFK_PROF_MARK(7)
       ok = mbar_wait_warp(bar_s_full + 8 * t, j & 1, actx, kErrFmhaSFull);
+      CFK_PROF_MARK(0)
       if (!ok) break;
       tc_fence_after_sync();
       tmem_ld_x32(tS + 0, sreg + 0);
@@ -290,26 +351,30 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_x32(tS + 64, sreg + 64);
       tmem_ld_x32(tS + 96, sreg + 96);
       tmem_wait_ld();
+      CFK_PROF_MARK(1)
 
-      // masking: columns beyond the causal limit of this row or beyond the key length
-      {
+      // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
+      // needs it at all depends only on the tile, so the test costs no vote.
+      if (j * C::BN + 127 > tile_min_lim) {
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }
         lim -= j * C::BN;     // last visible local column
-        if (__any_sync(0xffffffffu, lim < 127)) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (i > lim) sreg[i] = 0xff800000u;  // -inf
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i > lim) sreg[i] = 0xff800000u;  // -inf
       }
 
-      float mx0 = __uint_as_float(sreg[0]), mx1 = __uint_as_float(sreg[1]);
+      // row maximum: sixteen independent chains of two-input max, then a tree
+      float mx[16];
 #pragma unroll
-      for (int i = 2; i < 128; i += 4) {
-        mx0 = fmax3(mx0, __uint_as_float(sreg[i]), __uint_as_float(sreg[i + 1]));
-        if (i + 3 < 128) mx1 = fmax3(mx1, __uint_as_float(sreg[i + 2]), __uint_as_float(sreg[i + 3]));
-      }
-      const float rowmax = fmaxf(mx0, mx1);
+      for (int i = 0; i < 16; ++i) mx[i] = __uint_as_float(sreg[i]);
+#pragma unroll
+      for (int i = 16; i < 128; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
+#pragma unroll
+      for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; ++i) mx[i] = fmaxf(mx[i], mx[i + w]);
+      const float rowmax = mx[0];
       m_true = fmaxf(m_true, rowmax);
 
       if (j == 0) {
@@ -336,59 +401,59 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_wait_st();
         }
       }
-
-      // P = 2^(x - m), summed unrounded into l, rounded to the GEMM-II operand type and written over
-      // S_t (all of S_t is in registers by now).  For bf16 rows that see few keys the rounding error of
-      // P is not averaged out, so P is kept as hi + lo (two bf16 terms, two MMAs).
+      CFK_PROF_MARK(2)
       const float negm = C::PSHIFT - m_ref * sl;
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+      auto gen_p = [&](auto split_c) {
+        constexpr bool SPLIT = decltype(split_c)::value;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        float2 pr[16];   // the 32 probabilities of this chunk, as pairs
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
+                                                  __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
+          pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+          if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
+        }
         if constexpr (C::PESZ == 2) {
           uint32_t hi[16], lo[16];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 2 * i + 0]), sl, negm));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 2 * i + 1]), sl, negm));
-            const float p2 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 2 * i + 2]), sl, negm));
-            const float p3 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 2 * i + 3]), sl, negm));
-            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+          for (int j = 0; j < 16; ++j) {
             if constexpr (PT == kDtBF16) {
-              hi[i] = pack_bf16x2(p0, p1);
-              hi[i + 1] = pack_bf16x2(p2, p3);
-              if (split) {
-                lo[i] = pack_bf16x2(p0 - __uint_as_float(hi[i] << 16), p1 - __uint_as_float(hi[i] & 0xffff0000u));
-                lo[i + 1] = pack_bf16x2(p2 - __uint_as_float(hi[i + 1] << 16),
-                                        p3 - __uint_as_float(hi[i + 1] & 0xffff0000u));
-              }
+              hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
+              if constexpr (SPLIT)
+                lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
             } else {
-              hi[i] = pack_f16x2(p0, p1);
-              hi[i + 1] = pack_f16x2(p2, p3);
+              hi[j] = pack_f16x2(pr[j].x, pr[j].y);
             }
           }
           tmem_st_x16(tS + 16 * c, hi);
           if constexpr (PT == kDtBF16) {
-            if (split) tmem_st_x16(tS + 64 + 16 * c, lo);
+            if constexpr (SPLIT) tmem_st_x16(tS + 64 + 16 * c, lo);
           }
         } else {
           uint32_t w[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 4 * i + 0]), sl, negm));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 4 * i + 1]), sl, negm));
-            const float p2 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 4 * i + 2]), sl, negm));
-            const float p3 = ex2_approx(fmaf(__uint_as_float(sreg[32 * c + 4 * i + 3]), sl, negm));
-            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
-            w[i] = pack_e4m3x4(p0, p1, p2, p3);
-          }
+          for (int j = 0; j < 8; ++j) w[j] = pack_e4m3x4(pr[2 * j].x, pr[2 * j].y, pr[2 * j + 1].x, pr[2 * j + 1].y);
           tmem_st_x8(tS + 8 * c, w);
         }
       }
-      l += (s0 + s1) + (s2 + s3);
+      };
+      if constexpr (PT == kDtBF16) {
+        if (split) gen_p(std::true_type{}); else gen_p(std::false_type{});
+      } else {
+        gen_p(std::false_type{});
+      }
+      l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+      CFK_PROF_MARK(3)
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p_full + 8 * t);
+      CFK_PROF_MARK(4)
     }
+    CFK_PROF_MARK(7)
 
     if (ok && n_my > 0) {
       ok = mbar_wait_warp(bar_o_full + 8 * t, 0, actx, kErrFmhaOFull);
@@ -435,6 +500,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
+    CFK_PROF_MARK(5)
+    CFK_PROF_FLUSH(0, 8, (tid == 0))
   }
 
   // ---- tear-down ----

@@ -13,6 +13,7 @@ struct FmhaLaunch {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   FmhaParams p;
   int iterations;
+  int exp_emu;   // 0..3: share (in quarters) of the exponentials computed on the FMA pipe
   cudaStream_t stream;
 };
 

@@ -14,6 +14,7 @@ struct FmhaParams {
   int causal;        // key j visible to query i iff j <= i + (Skv - Sq)
   int out_bf16;      // output element type: 0 fp16, 1 bf16
   int nqblk;         // number of 256-row query blocks
+  int group;         // (batch, head) pairs scheduled side by side (their K and V share L2)
   int split_keys;    // bf16: CTAs whose first row sees fewer keys than this keep P as hi + lo (0 = never)
   float scale_log2;  // softmax_scale * log2(e) * q_descale * k_descale
   float out_scale;   // v_descale

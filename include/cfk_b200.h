@@ -123,6 +123,19 @@ int cfk_device_status(int* code_out);
 /* Text of the last CUDA runtime error seen by this library on the calling thread ("" if none). */
 const char* cfk_last_cuda_error(void);
 
+/*
+ * Tuning knobs, process-wide; the defaults are the values measured best on B200 and a negative value
+ * restores the default.  No counterpart in the reference, whose knobs are compile-time macros
+ * (src/fmha-pipeline/shared_storage.h:3-32).
+ *   CFK_TUNE_FMHA_EXP_EMU   0..3: of every four pairs of softmax exponentials, how many are evaluated
+ *                           with a cubic on the FMA pipe instead of the special-function unit.
+ *   CFK_TUNE_FMHA_GROUP_MB  causal only: heads are scheduled in groups whose K and V total at most
+ *                           this many MiB (so they share L2), heaviest query blocks first.
+ */
+enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_COUNT = 2 };
+int cfk_set_tunable(int which, int value);
+int cfk_get_tunable(int which); /* -1 for an unknown knob */
+
 /* Library version, e.g. 100 = 0.1.0. */
 int cfk_version(void);
 
