@@ -46,8 +46,8 @@ def test_gemm_batched(lib, oracle, cuda):
 
 
 def test_gemm_linearity_at_full_size(lib, cuda):
-    """8192^3 (the baseline's GEMM config): C(alpha=2) == 2 * C(alpha=1) exactly in fp16 (power-of-two
-    scaling commutes with rounding while nothing overflows), and a sampled set of entries equals an
+    """8192^3 (the baseline's GEMM config): C(alpha=2) == 2 * C(alpha=1) in fp16 (power-of-two scaling
+    commutes with rounding while nothing overflows or is subnormal), and a sampled set of entries equals an
     fp64 dot product of the same operands to fp16 rounding."""
     n = 8192
     torch.manual_seed(1)
@@ -58,7 +58,8 @@ def test_gemm_linearity_at_full_size(lib, cuda):
     lib.gemm(a, b, c1, dtype=0, m=n, n=n, k=n)
     lib.gemm(a, b, c2, dtype=0, m=n, n=n, k=n, alpha=2.0)
     lib.check_device()
-    assert torch.equal(c2, c1 * 2)
+    # exact except where the result is an fp16 subnormal (fixed spacing 2^-24 there)
+    assert (c2.float() - 2 * c1.float()).abs().max().item() <= 2.0 ** -23
     idx = torch.randint(0, n, (64, 2))
     for m, nn in idx.tolist():
         ref = float(a[m].double() @ b[nn].double())
