@@ -18,9 +18,9 @@ FP16, BF16, E4M3, FP32 = 0, 1, 2, 3
 DTYPES = {"fp16": FP16, "bf16": BF16, "e4m3": E4M3, "fp32": FP32}
 
 STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4: "LAUNCH", 5: "NO_DRIVER",
-                6: "DEVICE_WAIT"}
+                6: "DEVICE_WAIT", 7: "TOO_LARGE"}
 
-EXPORTS = ["cfk_fmha_forward", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
+EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
            "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_set_tunable", "cfk_get_tunable"]
 
 TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB = 0, 1
@@ -73,6 +73,7 @@ class CfkLib:
         self.lib = C.CDLL(path)
         L = self.lib
         L.cfk_fmha_forward.argtypes = [C.POINTER(FmhaArgs), C.c_void_p]
+        L.cfk_fmha_forward_static.argtypes = [C.POINTER(FmhaArgs), C.c_void_p]
         L.cfk_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
         L.cfk_fill.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_int64, C.c_int, C.c_float, C.c_float,
                                C.c_void_p]
@@ -84,6 +85,9 @@ class CfkLib:
     # -- raw calls (return the status code) ---------------------------------------------------
     def fmha_forward_raw(self, args: FmhaArgs, stream=None) -> int:
         return int(self.lib.cfk_fmha_forward(C.byref(args), stream))
+
+    def fmha_forward_static_raw(self, args: FmhaArgs, stream=None) -> int:
+        return int(self.lib.cfk_fmha_forward_static(C.byref(args), stream))
 
     def gemm_raw(self, args: GemmArgs, stream=None) -> int:
         return int(self.lib.cfk_gemm(C.byref(args), stream))

@@ -29,7 +29,8 @@ enum cfk_status {
   CFK_ERR_DESCRIPTOR = 3,    /* the driver refused a TMA descriptor */
   CFK_ERR_LAUNCH = 4,        /* cudaFuncSetAttribute / launch failed; see cfk_last_cuda_error */
   CFK_ERR_NO_DRIVER = 5,     /* no CUDA driver / device */
-  CFK_ERR_DEVICE_WAIT = 6    /* a bounded wait inside a kernel gave up; see cfk_device_status */
+  CFK_ERR_DEVICE_WAIT = 6,   /* a bounded wait inside a kernel gave up; see cfk_device_status */
+  CFK_ERR_TOO_LARGE = 7      /* the call needs more scratch than a fixed-capacity entry point holds */
 };
 
 /*
@@ -77,6 +78,26 @@ typedef struct cfk_fmha_args {
 } cfk_fmha_args;
 
 int cfk_fmha_forward(const cfk_fmha_args* args, cfk_stream_t stream);
+
+/*
+ * The same forward pass for callers that are not allowed to allocate device memory.  (This entry point
+ * has no counterpart in the reference, whose launchers never allocate because they keep no device state.)
+ *
+ * cfk_fmha_forward obtains its 256-byte status block with cudaMalloc the first time a device is used,
+ * which also synchronises the device.  That rules it out in a server that has given all of HBM to its
+ * own pool (even 256 bytes can fail or fragment there), in latency-bound loops that cannot take the
+ * device-wide synchronisation, and wherever allocation after start-up is forbidden.  This variant
+ * runs the same kernels with that scratch in a fixed 256-byte array inside the library image (one copy
+ * per GPU that loads the library, held until the process exits) and calls no allocating routine.
+ *   - Arguments, checks, kernels and results are those of cfk_fmha_forward.
+ *   - The first call on a device looks up the array's device address; make it before any capture starts.
+ *   - The array is shared by all calls on a device and keeps the last call's contents; the status word is
+ *     cleared on `stream` before the launches.  Calls whose kernels overlap on the GPU race on it.
+ *   - A build whose kernels need more scratch than the array holds is refused with CFK_ERR_TOO_LARGE.
+ *   - iterations == 0 launches nothing: it waits for `stream` and returns CFK_ERR_DEVICE_WAIT if the status
+ *     word left by the preceding call is non-zero (cfk_device_status reads the allocated block only).
+ */
+int cfk_fmha_forward_static(const cfk_fmha_args* args, cfk_stream_t stream);
 
 /*
  * GEMM:  C[m,n] = alpha * sum_k A[m,k] * B[n,k] + beta * C[m,n], fp32 accumulation, batched over L.

@@ -1,0 +1,52 @@
+"""cfk_fmha_forward_static: the forward pass for callers that may not allocate device memory (servers
+whose own pool owns all of HBM, latency-bound loops, hosts that forbid allocation after start-up).  It must
+give what cfk_fmha_forward gives, call after call, although its scratch is one shared array that keeps
+the previous call's contents.  Collected last on purpose: a stop-at-first-failure run has then already
+been through every other test."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import make_qkv
+
+pytestmark = pytest.mark.gpu
+
+
+def _args(lib, low, o, scales, dtype, causal, iterations=1):
+    q, k, v = low
+    B, S, H, D = q.shape
+    return lib.fmha_args(q, k, v, o, dtype=dtype, batch=B, heads=H, seqlen_q=S, seqlen_kv=k.shape[1], head_dim=D,
+                         softmax_scale=1.0 / math.sqrt(D), causal=causal, q_descale=scales[0], k_descale=scales[1],
+                         v_descale=scales[2], iterations=iterations)
+
+
+@pytest.mark.parametrize("dtype,causal", [(0, True), (1, False), (2, False)])
+def test_static_entry_point_matches_the_allocating_one_twice(lib, cuda, dtype, causal):
+    low, _, scales = make_qkv(dtype, 2, 1024, 1024, 3, 128, seed=31 + dtype)
+    low = [x.cuda() for x in low]
+    want = torch.full((2, 1024, 3, 128), -1.0, device="cuda", dtype=torch.float16)
+    assert lib.fmha_forward_raw(_args(lib, low, want, scales, dtype, causal)) == 0
+    lib.check_device()
+    for call in range(2):     # the second call finds the scratch as the first one left it
+        got = torch.full_like(want, -2.0)
+        assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, dtype, causal)) == 0
+        # iterations == 0: wait for the stream and report the status word of the call before
+        assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, dtype, causal, iterations=0)) == 0
+        # same kernels, same inputs: the tolerance of the other tests (2e-3) is met with zero difference
+        diff = (got.float() - want.float()).abs().max().item()
+        assert diff <= 2e-3, (call, diff)
+        assert torch.equal(got, want), call
+
+
+def test_static_entry_point_rejects_what_the_other_rejects(lib, cuda):
+    low, _, scales = make_qkv(0, 1, 128, 128, 1, 64, seed=1)
+    low = [x.cuda() for x in low]
+    o = torch.zeros(1, 128, 1, 64, device="cuda", dtype=torch.float16)
+    a = _args(lib, low, o, scales, 0, False)
+    a.head_dim = 96
+    assert lib.fmha_forward_static_raw(a) == 2
+    a = _args(lib, low, o, scales, 0, False)
+    a.o = None
+    assert lib.fmha_forward_static_raw(a) == 1
