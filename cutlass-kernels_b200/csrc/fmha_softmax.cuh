@@ -1,0 +1,218 @@
+// Pieces shared by the FMHA forward kernels (single-CTA and CTA-pair): tile configuration, the exp2
+// variants, the per-tile softmax step of a row-owning thread, and the staging of an output tile.
+// Reference counterparts: online_softmax.h:87-207 (onlineSoftmaxAndRescale), fmha_consumer.h:54 (P is
+// rounded to the GEMM-II operand type, unnormalised), fmha_epilogue.h:120-177 (normalise, stage, TMA store).
+#pragma once
+#include <type_traits>
+
+#include "common.cuh"
+#include "fmha_params.h"
+
+namespace cfk {
+
+template <int DT, int PT, int HD>
+struct FmhaCfg {
+  static constexpr int ESZ = (DT == kDtE4M3) ? 1 : 2;
+  static constexpr int PESZ = (PT == kDtE4M3) ? 1 : 2;
+  static_assert(ESZ == PESZ, "P and V must share an MMA kind");
+  static constexpr bool KIND8 = (ESZ == 1);
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int ROWB = HD * ESZ;            // bytes per row of a Q/K/V tile
+  static_assert(ROWB % 128 == 0, "rows must be whole 128-byte swizzle spans");
+  static constexpr int NSUB = ROWB / 128;          // 128-byte wide sub-tiles per tile
+  static constexpr int SUBB = 128 * 128;           // bytes per sub-tile (128 rows x 128 B)
+  static constexpr int TILEB = NSUB * SUBB;        // bytes per Q/K/V tile
+  static constexpr int ONSUB = HD * 2 / 128;       // output is always 16 bit
+  static constexpr int OTILEB = ONSUB * SUBB;
+  static constexpr bool O_SEPARATE = (OTILEB > TILEB);  // else O is staged over the Q tile
+  static constexpr int SMEM_LIMIT = 232448;
+  static constexpr int FIXEDB = 2 * TILEB + (O_SEPARATE ? 2 * OTILEB : 0);
+  static constexpr int BARB = 512;
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - 1024 - BARB - FIXEDB) / TILEB;
+  static constexpr int NSLOT = NSLOT_FIT > 8 ? 8 : NSLOT_FIT;
+  static_assert(NSLOT >= 3, "ring too small");
+  static constexpr int SMEM_BYTES = 1024 + FIXEDB + NSLOT * TILEB + BARB;
+  static constexpr int QK_KSTEPS = ROWB / 32;      // each UMMA consumes 32 bytes of K extent
+  static constexpr int PV_KSTEPS = BN * ESZ / 32;
+  static constexpr int V_STEPB = (32 / ESZ) * 128; // bytes between successive 32-byte-K groups of V rows
+  static constexpr int PCOLS = BN * PESZ / 4;      // TMEM columns taken by P
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int O_COL0 = 256;
+  static constexpr uint32_t FMT_IN = (DT == kDtBF16) ? kFmtBF16 : 0u;   // f16 / e4m3 are both code 0
+  static constexpr uint32_t FMT_P = (PT == kDtBF16) ? kFmtBF16 : 0u;
+  static constexpr uint32_t IDESC_QK = make_idesc(1, FMT_IN, FMT_IN, 0, 0, BM, BN);
+  static constexpr uint32_t IDESC_PV = make_idesc(1, FMT_P, FMT_IN, 0, 1, BM, HD);
+  static constexpr int NTHREADS = 384;
+  // Register budget after setmaxnreg.  The pool is what the CTA was launched with: 384 threads at the
+  // 168 registers a 384-thread launch bound allows.  setmaxnreg.inc blocks until the registers it asks
+  // for are free, with no time limit, so the sum below must never exceed that pool.
+  static constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 216, AUX_REGS = 72;
+  static_assert(2 * 128 * SOFTMAX_REGS + 128 * AUX_REGS <= NTHREADS * LAUNCH_REGS, "setmaxnreg would block forever");
+  // log2-domain slack before the running maximum is moved, and a constant exponent offset that puts
+  // P into the well-represented range of its type (it cancels in O / l).
+  static constexpr float TAU = (PT == kDtE4M3) ? 2.0f : 8.0f;
+  static constexpr float PSHIFT = (PT == kDtE4M3) ? 6.0f : 0.0f;
+};
+
+// exp2 of a pair of log2-domain scores on the special-function unit ...
+__device__ __forceinline__ float2 exp2_pair_sfu(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
+// ... or on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic whose relative
+// error (7.5e-5) is below the rounding step of every P format; 2^n by adding n to the exponent bits.
+// The special-function unit delivers 16 results per clock per SM, exactly what the tensor core consumes
+// at D=128, so a share of the exponentials is moved here (packed two-wide FMA instructions).
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));      // 1.5 * 2^23: n sits in the low bits
+  const float2 nf = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
+  float2 q = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+  q = __ffma2_rn(q, f, make_float2(0.6932609677f, 0.6932609677f));
+  q = __ffma2_rn(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return q;
+}
+
+// Optional per-role cycle counters (build with -DCFK_FMHA_PROFILE): lane 0 of the first warp of softmax
+// warpgroup 0 and the UMMA thread add the cycles they spend in each phase to words 8.. of the status
+// block.  Off in the shipped library.
+#ifdef CFK_FMHA_PROFILE
+#define CFK_PROF_DECL(n) long long prof_t[n] = {0}; long long prof_last = clock64();
+#define CFK_PROF_MARK(i) { const long long now_ = clock64(); prof_t[i] += now_ - prof_last; prof_last = now_; }
+#define CFK_PROF_FLUSH(base, n, cond) if (cond) { for (int i_ = 0; i_ < n; ++i_) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + base + i_, (unsigned long long)prof_t[i_]); }
+#else
+#define CFK_PROF_DECL(n)
+#define CFK_PROF_MARK(i)
+#define CFK_PROF_FLUSH(base, n, cond)
+#endif
+
+// One key tile of the online softmax for the thread that owns a query row.  On entry sreg[0..127] holds
+// the row's raw scores (S_t, fp32 bits); on exit P has been written over S_t in tensor memory (tcgen05.st
+// issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first key tile of the row;
+// `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible column.
+template <class CFG, int PT, int HD, int EMU>
+__device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tO, float sl, bool first,
+                                       bool mask_tile, int lim, bool split, float& m_ref, float& m_true,
+                                       float& l) {
+  // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
+  // needs it at all depends only on the tile, so the test costs no vote.
+  if (mask_tile) {   // lim: last visible local column of this row
+#pragma unroll
+    for (int i = 0; i < 128; ++i)
+      if (i > lim) sreg[i] = 0xff800000u;  // -inf
+  }
+
+  // row maximum: sixteen independent chains of two-input max, then a tree
+  float mx[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) mx[i] = __uint_as_float(sreg[i]);
+#pragma unroll
+  for (int i = 16; i < 128; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
+#pragma unroll
+  for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+    for (int i = 0; i < w; ++i) mx[i] = fmaxf(mx[i], mx[i + w]);
+  const float rowmax = mx[0];
+  m_true = fmaxf(m_true, rowmax);
+
+  if (first) {
+    m_ref = (rowmax == -INFINITY) ? 0.f : rowmax;
+  } else {
+    const bool need = (rowmax - m_ref) * sl > CFG::TAU;
+    if (__any_sync(0xffffffffu, need)) {
+      float alpha = 1.f;
+      if (need) {
+        alpha = ex2_approx((m_ref - rowmax) * sl);
+        m_ref = rowmax;
+        l *= alpha;
+      }
+      // O_t is complete up to tile j-1 here: the commit that released S_t(j) was issued after it.
+      uint32_t oreg[32];
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        tmem_ld_x32(tO + c * 32, oreg);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+        tmem_st_x32(tO + c * 32, oreg);
+      }
+      tmem_wait_st();
+    }
+  }
+  CFK_PROF_MARK(2)
+  const float negm = CFG::PSHIFT - m_ref * sl;
+  const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
+  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+  auto gen_p = [&](auto split_c) {
+    constexpr bool SPLIT = decltype(split_c)::value;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float2 pr[16];   // the 32 probabilities of this chunk, as pairs
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
+                                              __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
+      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+      if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
+    }
+    if constexpr (CFG::PESZ == 2) {
+      uint32_t hi[16], lo[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if constexpr (PT == kDtBF16) {
+          hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
+          if constexpr (SPLIT)
+            lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
+        } else {
+          hi[j] = pack_f16x2(pr[j].x, pr[j].y);
+        }
+      }
+      tmem_st_x16(tS + 16 * c, hi);
+      if constexpr (PT == kDtBF16) {
+        if constexpr (SPLIT) tmem_st_x16(tS + 64 + 16 * c, lo);
+      }
+    } else {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = pack_e4m3x4(pr[2 * j].x, pr[2 * j].y, pr[2 * j + 1].x, pr[2 * j + 1].y);
+      tmem_st_x8(tS + 8 * c, w);
+    }
+  }
+  };
+  if constexpr (PT == kDtBF16) {
+    if (split) gen_p(std::true_type{}); else gen_p(std::false_type{});
+  } else {
+    gen_p(std::false_type{});
+  }
+  l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
+}
+
+// O_t (fp32, tensor memory) * inv -> 16 bit -> shared-memory tile in the 128-byte swizzled layout the TMA
+// store reads ([64-column span][row][128 B]); `r` is this thread's row.
+template <class CFG, int HD>
+__device__ __forceinline__ void stage_output(uint32_t tO, uint32_t stage, int r, float inv, bool out_bf16) {
+                    uint32_t oreg[32];
+#pragma unroll
+    for (int c = 0; c < HD / 32; ++c) {
+      tmem_ld_x32(tO + c * 32, oreg);
+      tmem_wait_ld();
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = __uint_as_float(oreg[2 * i]) * inv, b = __uint_as_float(oreg[2 * i + 1]) * inv;
+        pk[i] = out_bf16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+      }
+      // 32 output columns = 64 bytes = four 16-byte chunks of sub-tile c/2, 128-byte swizzled
+      const uint32_t row_addr = stage + (c >> 1) * CFG::SUBB + r * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t chunk = (uint32_t)((c & 1) * 4 + i) ^ (uint32_t)(r & 7);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16), "r"(pk[4 * i]),
+                     "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                     : "memory");
+      }
+    }
+}
+
+}  // namespace cfk

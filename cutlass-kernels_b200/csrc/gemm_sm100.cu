@@ -2,17 +2,22 @@
 // K-contiguous, D row-major with leading dimension ldd, fp32 accumulation in tensor memory.
 // It stands where the reference has gemm<> / gemm_device (src/cute-gemm-tma-gma/gemm.cu:336-463,
 // 57-334): that kernel is a single-stage TMA -> WGMMA loop that stores register accumulators straight
-// to global memory, ignores alpha / beta and accumulates in the output type.  Here:
+// to global memory, ignores alpha / beta and accumulates in the output type.  Here a pair of CTAs on two
+// SMs (a cluster of 2, tcgen05 cta_group::2) computes a 256 x 256 tile:
 //
-//   warp 0     TMA producer: X (128 x 64) and Y (256 x 64) tiles into a multi-stage ring
-//   warp 1     UMMA issuer: 128 x 256 x 16 tcgen05.mma, two accumulator buffers of 256 TMEM columns
-//   warps 2-5  epilogue: TMEM -> registers -> alpha/beta -> 16-bit -> global, overlapped with the
-//              next tile's main loop
+//   warp 0     TMA producer: this CTA's 128 rows of X and its 128 rows of Y per 64-wide k-block, into a
+//              6-stage ring; both CTAs signal the same barrier in the leader (no multicast: each CTA
+//              fetches only what its own SM consumes)
+//   warp 1     UMMA issuer (leader CTA only): 256 x 256 x 16 tcgen05.mma over the pair, two accumulator
+//              buffers of 256 TMEM columns per CTA
+//   warps 2-5  epilogue: TMEM -> registers -> alpha/beta -> 16-bit -> global, overlapped with the next
+//              tile's main loop
 //
-// CTAs are persistent (one per SM) and walk the tile list in bands of 8 row-tiles so that
-// concurrently running tiles share X and Y panels in L2.  The reference's column-major C
-// (gemm.cu:388-389) is the row-major D of the swapped problem (X = B, Y = A), so one kernel serves
-// both output orders.
+// The pair halves the B-operand bytes each SM reads from shared memory per FLOP, which is what bounds a
+// single-CTA 128 x 256 tile.  Pairs are persistent (one per two SMs) and walk the tile list in bands of
+// 4 row-tiles so that concurrently running tiles share X and Y panels in L2.  The reference's column-major
+// C (gemm.cu:388-389) is the row-major D of the swapped problem (X = B, Y = A), so one kernel serves both
+// output orders.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -32,17 +37,18 @@ struct GemmParams {
   void* d;
   float alpha, beta;
   int bf16;
-  int tiles_r, tiles_c;
+  int tiles_r, tiles_c;  // 256 x 256 tiles
   int* status;
 };
 
 struct GemmCfg {
-  static constexpr int BM = 128, BN = 256, BK = 64;
-  static constexpr int XB = BM * BK * 2, YB = BN * BK * 2;   // bytes per stage
-  static constexpr int NSTAGE = 4;
+  static constexpr int BM = 128, BNH = 128, BK = 64;         // per CTA: rows of X, rows of Y, k extent
+  static constexpr int TILE = 256;                            // tile edge of the CTA pair
+  static constexpr int XB = BM * BK * 2, YB = BNH * BK * 2;   // bytes per stage
+  static constexpr int NSTAGE = 6;
   static constexpr int SMEM_BYTES = 1024 + NSTAGE * (XB + YB) + 256;
   static constexpr int NTHREADS = 192;
-  static constexpr int BAND = 8;
+  static constexpr int BAND = 4;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, int& tr, int& tc, int& batch) {
@@ -58,7 +64,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, 
   tc = t / rows_in_band;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y, const GemmParams p) {
   using C = GemmCfg;
   extern __shared__ uint8_t smem_raw[];
@@ -67,10 +73,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
   const uint32_t sX = smem_base;
   const uint32_t sY = smem_base + C::NSTAGE * C::XB;
   const uint32_t sBar = sY + C::NSTAGE * C::YB;
-  const uint32_t bar_full = sBar;                       // [NSTAGE]
-  const uint32_t bar_empty = sBar + 8 * C::NSTAGE;      // [NSTAGE]
-  const uint32_t bar_acc_full = bar_empty + 8 * C::NSTAGE;  // [2]
-  const uint32_t bar_acc_empty = bar_acc_full + 16;         // [2]
+  const uint32_t bar_full = sBar;                            // [NSTAGE] leader: both CTAs' loads of a stage landed
+  const uint32_t bar_empty = sBar + 8 * C::NSTAGE;           // [NSTAGE] each CTA: its stage was consumed
+  const uint32_t bar_acc_full = bar_empty + 8 * C::NSTAGE;   // [2] each CTA: accumulator complete
+  const uint32_t bar_acc_empty = bar_acc_full + 16;          // [2] leader: both epilogues have read it
   uint8_t* gBar = smem_gen + (sBar - smem_base);
   const uint32_t off_misc = 8 * (2 * C::NSTAGE + 4);
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
@@ -78,23 +84,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
   const AbortCtx actx{s_abort, p.status};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int total_tiles = p.tiles_r * p.tiles_c * p.L;
   const int nkb = (p.K + C::BK - 1) / C::BK;
 
+  // Both CTAs of a pair read the same word, so they skip or run together.
   if (cta_should_skip(p.status)) return;
   if (tid == 0) {
-    for (int i = 0; i < C::NSTAGE; ++i) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 128); }
+    for (int i = 0; i < C::NSTAGE; ++i) { mbar_init(bar_full + 8 * i, 2); mbar_init(bar_empty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 256); }
     *s_abort = 0u;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 512);
-    tmem_relinquish();
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 512);
+    tmem_relinquish_pair();
   }
   if (warp == 0 && lane == 0) { tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_y); }
   tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all();           // the peer's barriers exist before anything is signalled on them
   tc_fence_after_sync();
   const uint32_t tmem_base = *s_tmem_base;
 
@@ -102,27 +112,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
     if (lane == 0) {
       int idx = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs) {
         int tr, tc, b;
         tile_coords(tile, p.tiles_r, p.tiles_c, tr, tc, b);
         for (int kb = 0; kb < nkb; ++kb, ++idx) {
           const int s = idx % C::NSTAGE;
           const uint32_t ph = (idx / C::NSTAGE) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, actx, kErrGemmEmpty)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_full + 8 * s, C::XB + C::YB);
-          tma_load_3d(sX + s * C::XB, &tm_x, bar_full + 8 * s, kb * C::BK, tr * C::BM, b);
-          tma_load_3d(sY + s * C::YB, &tm_y, bar_full + 8 * s, kb * C::BK, tc * C::BN, b);
+          const uint32_t leader_full = map_to_cta(bar_full + 8 * s, 0);
+          mbar_arrive_expect_tx_cluster(leader_full, C::XB + C::YB);
+          tma_load_3d_pair(sX + s * C::XB, &tm_x, leader_full, kb * C::BK, tr * C::TILE + (int)rank * C::BM, b);
+          tma_load_3d_pair(sY + s * C::YB, &tm_y, leader_full, kb * C::BK, tc * C::TILE + (int)rank * C::BNH, b);
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_f16 = make_idesc(1, kFmtF16, kFmtF16, 0, 0, C::BM, C::BN);
-      constexpr uint32_t idesc_bf16 = make_idesc(1, kFmtBF16, kFmtBF16, 0, 0, C::BM, C::BN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc_f16 = make_idesc(1, kFmtF16, kFmtF16, 0, 0, C::TILE, C::TILE);
+      constexpr uint32_t idesc_bf16 = make_idesc(1, kFmtBF16, kFmtBF16, 0, 0, C::TILE, C::TILE);
       const uint32_t idesc = p.bf16 ? idesc_bf16 : idesc_f16;
       int idx = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
         const int buf = local & 1;
         const uint32_t acc_ph = (local >> 1) & 1;
         if (!mbar_wait(bar_acc_empty + 8 * buf, acc_ph ^ 1u, actx, kErrGemmAccEmpty)) { ok = false; break; }
@@ -136,31 +147,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
           const uint64_t b0 = make_smem_desc(sY + s * C::YB, 16, 1024, kSwizzle128B);
 #pragma unroll
           for (int kk = 0; kk < C::BK / 16; ++kk)
-            umma_ss<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
-          umma_commit(bar_empty + 8 * s);
+            umma_ss_pair<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc,
+                                (kb | kk) != 0 ? 1u : 0u);
+          umma_commit_pair(bar_empty + 8 * s);                  // this CTA's stage
+          umma_commit_pair(map_to_cta(bar_empty + 8 * s, 1));   // the peer's stage
         }
-        if (ok) umma_commit(bar_acc_full + 8 * buf);
+        if (ok) {
+          umma_commit_pair(bar_acc_full + 8 * buf);
+          umma_commit_pair(map_to_cta(bar_acc_full + 8 * buf, 1));
+        }
       }
     }
   } else {
     // epilogue warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31
     const int q = warp & 3;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    const int row_in_tile = q * 32 + lane;
+    const int row_in_tile = (int)rank * C::BM + q * 32 + lane;
+    const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
       int tr, tc, b;
       tile_coords(tile, p.tiles_r, p.tiles_c, tr, tc, b);
       const int buf = local & 1;
       ok = mbar_wait_warp(bar_acc_full + 8 * buf, (local >> 1) & 1, actx, kErrGemmAccFull);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = tr * C::BM + row_in_tile;
-      const int col0 = tc * C::BN;
+      const int row = tr * C::TILE + row_in_tile;
+      const int col0 = tc * C::TILE;
       uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
 #pragma unroll 1
-      for (int c = 0; c < C::BN / 32; ++c) {
+      for (int c = 0; c < C::TILE / 32; ++c) {
         uint32_t acc[32];
         tmem_ld_x32(tmem_base + lane_base + buf * 256 + c * 32, acc);
         tmem_wait_ld();
@@ -205,15 +222,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(bar_acc_empty + 8 * buf);
+      mbar_arrive_cluster(leader_acc_empty + 8 * buf);
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all();           // no CTA leaves while its peer may still read its shared memory or signal it
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -242,10 +260,10 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   CUtensorMap tm_x, tm_y;
   const uint64_t xd[3] = {(uint64_t)a->k, (uint64_t)R, (uint64_t)a->l};
   const uint64_t xs[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)R};
-  const uint32_t xb[3] = {GemmCfg::BK, GemmCfg::BM, 1};
+  const uint32_t xb[3] = {GemmCfg::BK, GemmCfg::BM, 1};       // per CTA: 128 rows of X
   const uint64_t yd[3] = {(uint64_t)a->k, (uint64_t)Cn, (uint64_t)a->l};
   const uint64_t ys[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)Cn};
-  const uint32_t yb[3] = {GemmCfg::BK, GemmCfg::BN, 1};
+  const uint32_t yb[3] = {GemmCfg::BK, GemmCfg::BNH, 1};      // per CTA: 128 rows of Y
   int rc;
   if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, true))) return rc;
   if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, true))) return rc;
@@ -258,8 +276,8 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   p.d = a->c;
   p.alpha = a->alpha; p.beta = a->beta;
   p.bf16 = a->dtype == CFK_BF16;
-  p.tiles_r = (R + GemmCfg::BM - 1) / GemmCfg::BM;
-  p.tiles_c = (Cn + GemmCfg::BN - 1) / GemmCfg::BN;
+  p.tiles_r = (R + GemmCfg::TILE - 1) / GemmCfg::TILE;
+  p.tiles_c = (Cn + GemmCfg::TILE - 1) / GemmCfg::TILE;
   p.status = status;
 
   static thread_local int attr_dev = -1;
@@ -276,7 +294,8 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   }
   const long long total = (long long)p.tiles_r * p.tiles_c * p.L;
   if (total > 0x7fffffffLL) return CFK_ERR_UNSUPPORTED;
-  const int grid = (int)(total < sm_count ? total : sm_count);
+  const long long pairs = total < sm_count / 2 ? total : sm_count / 2;   // one CTA pair per two SMs
+  const int grid = (int)(2 * pairs);
   for (int it = 0; it < a->iterations; ++it)
     gemm_kernel<<<grid, GemmCfg::NTHREADS, GemmCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tm_x, tm_y, p);
   return note_cuda(cudaGetLastError(), "gemm launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
