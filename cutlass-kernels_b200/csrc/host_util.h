@@ -29,6 +29,6 @@ int encode_tiled(CUtensorMap* map, int dtype, int rank, const void* base, const 
 // {128-byte span, seq, spans per row, head, batch}; a box is {span, box_rows, all spans, 1, 1}, so
 // one copy lands in shared memory as [span][row][128 B] with the 128-byte swizzle applied.
 int encode_bshd(CUtensorMap* map, int dtype, const void* base, int batch, int seq, int heads, int d, int64_t sb,
-                int64_t ss, int64_t sh, int box_rows);
+                int64_t ss, int64_t sh, int box_rows, int box_spans = 0 /* 0 = all spans of a row */);
 
 }  // namespace cfk
