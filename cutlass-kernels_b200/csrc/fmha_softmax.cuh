@@ -192,27 +192,27 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
 // store reads ([64-column span][row][128 B]); `r` is this thread's row.
 template <class CFG, int HD>
 __device__ __forceinline__ void stage_output(uint32_t tO, uint32_t stage, int r, float inv, bool out_bf16) {
-                    uint32_t oreg[32];
+  uint32_t oreg[32];
 #pragma unroll
-    for (int c = 0; c < HD / 32; ++c) {
-      tmem_ld_x32(tO + c * 32, oreg);
-      tmem_wait_ld();
-      uint32_t pk[16];
+  for (int c = 0; c < HD / 32; ++c) {
+    tmem_ld_x32(tO + c * 32, oreg);
+    tmem_wait_ld();
+    uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float a = __uint_as_float(oreg[2 * i]) * inv, b = __uint_as_float(oreg[2 * i + 1]) * inv;
-        pk[i] = out_bf16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
-      }
-      // 32 output columns = 64 bytes = four 16-byte chunks of sub-tile c/2, 128-byte swizzled
-      const uint32_t row_addr = stage + (c >> 1) * CFG::SUBB + r * 128;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t chunk = (uint32_t)((c & 1) * 4 + i) ^ (uint32_t)(r & 7);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16), "r"(pk[4 * i]),
-                     "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
-                     : "memory");
-      }
+    for (int i = 0; i < 16; ++i) {
+      const float a = __uint_as_float(oreg[2 * i]) * inv, b = __uint_as_float(oreg[2 * i + 1]) * inv;
+      pk[i] = out_bf16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
     }
+    // 32 output columns = 64 bytes = four 16-byte chunks of sub-tile c/2, 128-byte swizzled
+    const uint32_t row_addr = stage + (c >> 1) * CFG::SUBB + r * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t chunk = (uint32_t)((c & 1) * 4 + i) ^ (uint32_t)(r & 7);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + chunk * 16), "r"(pk[4 * i]),
+                   "r"(pk[4 * i + 1]), "r"(pk[4 * i + 2]), "r"(pk[4 * i + 3])
+                   : "memory");
+    }
+  }
 }
 
 }  // namespace cfk

@@ -135,15 +135,6 @@ extern "C" int cfk_fmha_forward_static(const cfk_fmha_args* a, cfk_stream_t stre
   if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
     return rc;
 
-  L.pair = (!fp8 && a->head_dim == 128 && cfk_get_tunable(CFK_TUNE_FMHA_CTA_PAIR) != 0) ? 1 : 0;
-  if (L.pair) {
-    if ((rc = encode_bshd(&L.tm_k_half, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 64)))
-      return rc;
-    if ((rc = encode_bshd(&L.tm_v_half, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, 1)))
-      return rc;
-  }
-  L.nqblk_pair = (a->seqlen_q + 511) / 512;
-
   FmhaParams& p = L.p;
   p.B = a->batch; p.H = a->heads; p.Sq = a->seqlen_q; p.Skv = a->seqlen_kv;
   p.causal = a->causal ? 1 : 0;

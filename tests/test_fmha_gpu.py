@@ -165,15 +165,3 @@ def test_fmha_large_logits_trigger_rescale(lib, oracle, cuda):
     # the output alone is 1.95e-3: the bound here is 2e-3 plus that rounding step
     check(oracle, got, stats, f32, 1.0 / math.sqrt(D), False, 0, max_abs=4e-3)
 
-
-@pytest.mark.parametrize("dtype,causal,S", [(0, False, 1024), (1, True, 2048), (0, True, 777)])
-def test_fmha_cta_pair_kernel_matches_oracle(lib, oracle, cuda, dtype, causal, S):
-    """The CTA-pair variant (two SMs share every K/V tile; off by default) gives the same answers."""
-    import cfk_b200
-    low, f32, scales = make_qkv(dtype, 1, S, S, 3, 128, seed=41)
-    lib.set_tunable(cfk_b200.TUNE_FMHA_CTA_PAIR, 1)
-    try:
-        got, stats = run_fmha(lib, low, scales, dtype, causal)
-    finally:
-        lib.set_tunable(cfk_b200.TUNE_FMHA_CTA_PAIR, -1)
-    check(oracle, got, stats, f32, 1.0 / math.sqrt(128), causal, dtype)
