@@ -39,6 +39,18 @@ DT_NAME = {0: "fp16", 1: "bf16", 2: "e4m3"}
 NOMINAL = {0: 2250.0, 1: 2250.0, 2: 4500.0}
 
 
+# DRAM bytes (read + write) of ONE launch of the FMHA kernel per workload, from one ncu capture of the CLI
+# driver on the same shape (the files under profiles/ give the commands).  The algorithmic bytes are Q + K + V
+# read once and O written once; the excess is K/V re-read by query blocks that missed them in L2.
+NCU_DRAM_BYTES_PER_LAUNCH = {"c4": 715.0e6, "c3": 253.3e6, "c5": 310.4e6}
+
+
+def algo_bytes_of(wl):
+    dt, B, H, S, D, causal, _ = wl
+    n = B * H * S * D
+    return n * (3 * (1 if dt == 2 else 2) + 2)     # Q, K, V in the input type; O in fp16
+
+
 def flops_of(B, H, S, D, causal):
     return 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
 
@@ -194,7 +206,7 @@ def run_reference(args, wl, rank, world):
         "impl": "reference", "metric": "fmha_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt_s / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": desc, "flop_convention": "4*B*H*S*S*D, halved for causal", "sample": sample},
+        "config": {"workload": desc, "accumulate": "fp32", "algorithmic_bytes_per_launch": algo_bytes_of(wl), "flop_convention": "4*B*H*S*S*D, halved for causal", "sample": sample},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": orc.threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -307,19 +319,14 @@ def main():
     # ---- rank 0: parity spot-check, CPU baseline, secondary configs ----
     burst, sustained, peak_kind = measured_peaks()
     per_gpu = step_flops / (ms * 1e-3) / 1e12
-    traffic = None
-    prof = os.path.join(ROOT, "profiles", "fmha_fwd_traffic.json")
-    if os.path.exists(prof):
-        try:
-            tj = json.load(open(prof))
-            traffic = tj.get(args.workload)
-        except (OSError, ValueError):
-            traffic = None
+    # DRAM bytes (read + write) of one kernel launch on this workload, from one ncu capture of the CLI driver
+    # on the same shape (profiles/fmha_fwd_*.md name the command); the algorithmic bytes are Q+K+V+O.
+    traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
     line = {
         "metric": "fmha_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": DT_NAME[dt] + " (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": desc, "flop_convention": "4*B*H*S*S*D, halved for causal",
+        "vs_baseline": None, "dtype": DT_NAME[dt], "data": "synthetic",
+        "config": {"workload": desc, "accumulate": "fp32", "algorithmic_bytes_per_launch": algo_bytes_of(wl), "flop_convention": "4*B*H*S*S*D, halved for causal",
                    "l2": "inputs (3 x %d MiB per GPU) exceed the 126 MB L2" % (q.numel() * q.element_size() >> 20),
                    "parallelism": "batch x head slices per GPU, no collective"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": burst, "unit": "TFLOP/s", "frac": per_gpu / burst,

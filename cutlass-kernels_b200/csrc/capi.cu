@@ -156,7 +156,7 @@ __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, int
 }
 
 // Tunables (process-wide).  Defaults are the measured best on B200.
-// EXP_EMU -1 = by type: 1 of 4 pairs for 16-bit inputs, 2 of 4 for e4m3 (measured best on B200).
+// EXP_EMU -1 = by type: none for 16-bit inputs, 1 of 4 pairs for e4m3 (measured best on B200).
 static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64};
 static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}};
 

@@ -190,6 +190,12 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_format, uint32_t a_
          ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// Same, touching only the low word (start address and leading offset share it, and the address field cannot
+// carry out of it): one 32-bit add instead of a 64-bit one on the single thread that issues every UMMA.
+__device__ __forceinline__ uint64_t desc_advance_lo(uint64_t d, uint32_t bytes) {
+  return (d & 0xffffffff00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(d) + (bytes >> 4));
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.  KIND8 selects kind::f8f6f4, else kind::f16.
 template <bool KIND8>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -226,6 +232,41 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
   }
 }
+// The same two instructions with the accumulate flag as a compile-time constant: the predicate folds away,
+// which matters because one thread issues every UMMA of the CTA while busy warps compete for issue slots.
+template <bool KIND8, int ACC>
+__device__ __forceinline__ void umma_ss_c(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
+  if constexpr (KIND8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "n"(ACC)
+        : "memory");
+  }
+}
+template <bool KIND8, int ACC>
+__device__ __forceinline__ void umma_ts_c(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+  if constexpr (KIND8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "n"(ACC)
+        : "memory");
+  }
+}
+
 // The mbarrier receives one arrival once every tcgen05 operation issued so far by this thread is done.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)

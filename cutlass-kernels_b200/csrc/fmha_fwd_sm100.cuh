@@ -164,30 +164,37 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================== UMMA issuer ===========================
     if (lane == 0 && n_kv > 0) {
       bool ok = true;
+      // Descriptor words that do not change: Q_0 and Q_1 (K-major), and ring slot 0 seen as a K tile
+      // (K-major) and as a V tile (MN-major: LBO = distance between the 64-element column groups, i.e. one
+      // sub-tile; SBO = distance between groups of 8 keys).  A slot or a k-step adds a constant to the low
+      // word.  The accumulate flag is a compile-time constant wherever it can be, so its predicate folds
+      // away: this one thread issues every UMMA while busy softmax warps compete for the same issue slots.
+      const uint64_t aq0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
+      const uint64_t bk0 = make_smem_desc(sRing, 16, 1024, kSwizzle128B);
+      const uint64_t bv0 = make_smem_desc(sRing, C::SUBB, 1024, kSwizzle128B);
       auto issue_qk = [&](int t, int slot) {
-        const uint64_t a0 = make_smem_desc(sQ + t * C::TILEB, 16, 1024, kSwizzle128B);
-        const uint64_t b0 = make_smem_desc(sRing + slot * C::TILEB, 16, 1024, kSwizzle128B);
+        const uint64_t a0 = desc_advance_lo(aq0, t * C::TILEB);
+        const uint64_t b0 = desc_advance_lo(bk0, slot * C::TILEB);
         const uint32_t d = tmem_base + t * 128;
+        umma_ss_c<C::KIND8, 0>(d, a0, b0, C::IDESC_QK);
 #pragma unroll
-        for (int kk = 0; kk < C::QK_KSTEPS; ++kk) {
+        for (int kk = 1; kk < C::QK_KSTEPS; ++kk) {
           const uint32_t off = (kk >> 2) * C::SUBB + (kk & 3) * 32;
-          umma_ss<C::KIND8>(d, desc_advance(a0, off), desc_advance(b0, off), C::IDESC_QK, kk > 0 ? 1u : 0u);
+          umma_ss_c<C::KIND8, 1>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK);
         }
       };
       auto issue_pv = [&](int t, int slot, uint32_t accumulate) {
-        // V tile: [NSUB][128 keys][128 B]; N (= d) contiguous.  LBO = distance between the 64-element
-        // column groups (one sub-tile), SBO = distance between groups of 8 keys.
-        const uint64_t b0 = make_smem_desc(sRing + slot * C::TILEB, C::SUBB, 1024, kSwizzle128B);
+        const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
         const uint32_t a = tmem_base + t * 128;
+        umma_ts<C::KIND8>(d, a, b0, C::IDESC_PV, accumulate);
 #pragma unroll
-        for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
-          umma_ts<C::KIND8>(d, a + kk * 8, desc_advance(b0, kk * C::V_STEPB), C::IDESC_PV,
-                            (accumulate | (uint32_t)(kk > 0)) ? 1u : 0u);
+        for (int kk = 1; kk < C::PV_KSTEPS; ++kk)
+          umma_ts_c<C::KIND8, 1>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV);
         if (split) {   // second term of P lives in the upper half of the S_t columns
 #pragma unroll
           for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
-            umma_ts<C::KIND8>(d, a + 64 + kk * 8, desc_advance(b0, kk * C::V_STEPB), C::IDESC_PV, 1u);
+            umma_ts_c<C::KIND8, 1>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV);
         }
       };
 
