@@ -178,7 +178,10 @@ def run_reference(args, wl, rank, world):
     the workload: `slices` whole (batch, head) problems of the same S, D and mask."""
     if rank != 0:
         return
-    import numpy as np
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; this arm is the only work of the job, so it takes
+    # every core the process may run on (the OpenMP runtime reads the variable when the oracle is loaded).
+    if "TORCHELASTIC_RUN_ID" in os.environ or world > 1:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     from oracle.oracle import CfkOracle
     orc = CfkOracle()
     dt, B, H, S, D, causal, desc = wl
