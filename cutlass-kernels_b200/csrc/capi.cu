@@ -156,9 +156,9 @@ __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, int
 }
 
 // Tunables (process-wide).  Defaults are the measured best on B200.
-// EXP_EMU -1 = by type: none for 16-bit inputs, 1 of 4 pairs for e4m3 (measured best on B200).
-static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64};
-static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}};
+// EXP_EMU -1 = by type: 1 of 4 pairs for 16-bit inputs, 2 of 4 for e4m3 (measured best on B200).
+static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64, 0};
+static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}, {0}};
 
 static bool valid_dtype(int dt) { return dt >= CFK_FP16 && dt <= CFK_FP32; }
 
@@ -173,6 +173,7 @@ extern "C" int cfk_set_tunable(int which, int value) {
   if (value < 0) value = kTunableDefault[which];
   if (which == CFK_TUNE_FMHA_EXP_EMU && value > 3) return CFK_ERR_INVALID_ARG;
   if (which == CFK_TUNE_FMHA_GROUP_MB && (value < 1 || value > 1024)) return CFK_ERR_INVALID_ARG;
+  if (which == CFK_TUNE_FMHA_CTA_PAIR && value > 1) return CFK_ERR_INVALID_ARG;
   g_tunable[which].store(value);
   return CFK_OK;
 }
@@ -277,6 +278,14 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
     return rc;
   if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
     return rc;
+
+  L.pair = (a->dtype != CFK_E4M3 && a->head_dim == 128 && g_tunable[CFK_TUNE_FMHA_CTA_PAIR].load() != 0) ? 1 : 0;
+  if (L.pair) {   // CTA-pair kernel: each CTA loads 64 keys of a K tile and one 64-column span of a V tile
+    if ((rc = encode_bshd(&L.tm_k_half, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 64)))
+      return rc;
+    if ((rc = encode_bshd(&L.tm_v_half, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, 1)))
+      return rc;
+  }
 
   FmhaParams& p = L.p;
   p.B = a->batch; p.H = a->heads; p.Sq = a->seqlen_q; p.Skv = a->seqlen_kv;

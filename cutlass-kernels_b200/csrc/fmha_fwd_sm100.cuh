@@ -107,7 +107,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1);
-      mbar_init(bar_p_full + 8 * t, 128);
+      mbar_init(bar_p_full + 8 * t, 4);
       mbar_init(bar_o_full + 8 * t, 1);
       mbar_init(bar_o_staged + 8 * t, 128);
     }
@@ -162,13 +162,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
    } else if (warp == 8) {
     // =========================== UMMA issuer ===========================
-    if (lane == 0 && n_kv > 0) {
+    // All 32 lanes run the loop (uniform control flow); one elected lane executes the tcgen05 instructions.
+    if (n_kv > 0) {
+      const uint32_t leader = elect_one();
       bool ok = true;
       // Descriptor words that do not change: Q_0 and Q_1 (K-major), and ring slot 0 seen as a K tile
       // (K-major) and as a V tile (MN-major: LBO = distance between the 64-element column groups, i.e. one
-      // sub-tile; SBO = distance between groups of 8 keys).  A slot or a k-step adds a constant to the low
-      // word.  The accumulate flag is a compile-time constant wherever it can be, so its predicate folds
-      // away: this one thread issues every UMMA while busy softmax warps compete for the same issue slots.
+      // sub-tile; SBO = distance between groups of 8 keys).  A slot or a k-step adds a constant to the low word.
       const uint64_t aq0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
       const uint64_t bk0 = make_smem_desc(sRing, 16, 1024, kSwizzle128B);
       const uint64_t bv0 = make_smem_desc(sRing, C::SUBB, 1024, kSwizzle128B);
@@ -176,76 +176,76 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint64_t a0 = desc_advance_lo(aq0, t * C::TILEB);
         const uint64_t b0 = desc_advance_lo(bk0, slot * C::TILEB);
         const uint32_t d = tmem_base + t * 128;
-        umma_ss_c<C::KIND8, 0>(d, a0, b0, C::IDESC_QK);
 #pragma unroll
-        for (int kk = 1; kk < C::QK_KSTEPS; ++kk) {
+        for (int kk = 0; kk < C::QK_KSTEPS; ++kk) {
           const uint32_t off = (kk >> 2) * C::SUBB + (kk & 3) * 32;
-          umma_ss_c<C::KIND8, 1>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK);
+          umma_ss_e<C::KIND8, false>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK, kk > 0 ? 1u : 0u,
+                                     leader);
         }
       };
       auto issue_pv = [&](int t, int slot, uint32_t accumulate) {
         const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
         const uint32_t a = tmem_base + t * 128;
-        umma_ts<C::KIND8>(d, a, b0, C::IDESC_PV, accumulate);
 #pragma unroll
-        for (int kk = 1; kk < C::PV_KSTEPS; ++kk)
-          umma_ts_c<C::KIND8, 1>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV);
+        for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
+          umma_ts_e<C::KIND8, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
+                                     kk > 0 ? 1u : accumulate, leader);
         if (split) {   // second term of P lives in the upper half of the S_t columns
 #pragma unroll
           for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
-            umma_ts_c<C::KIND8, 1>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV);
+            umma_ts_e<C::KIND8, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
         }
       };
 
       CFK_PROF_DECL(4)
-      ok = mbar_wait(bar_q_full, 0, actx, kErrFmhaQFull);
-      if (ok) ok = mbar_wait(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
+      ok = mbar_wait_warp(bar_q_full, 0, actx, kErrFmhaQFull);
+      if (ok) ok = mbar_wait_warp(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
       CFK_PROF_MARK(0)
       if (ok) {
         tc_fence_after_sync();
         for (int t = 0; t < 2; ++t)
           if (n_of(t) > 0) {
             issue_qk(t, 0);
-            umma_commit(bar_s_full + 8 * t);
+            umma_commit_e<false>(bar_s_full + 8 * t, leader);
           }
-        umma_commit(bar_kv_empty + 0);
+        umma_commit_e<false>(bar_kv_empty + 0, leader);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
         CFK_PROF_MARK(3)
-        ok = mbar_wait(bar_kv_full + 8 * vslot, (vidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+        ok = mbar_wait_warp(bar_kv_full + 8 * vslot, (vidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
         CFK_PROF_MARK(1)
         bool k_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_of(t)) continue;
           CFK_PROF_MARK(3)
-          ok = mbar_wait(bar_p_full + 8 * t, j & 1, actx, kErrFmhaPFull);
+          ok = mbar_wait_warp(bar_p_full + 8 * t, j & 1, actx, kErrFmhaPFull);
           CFK_PROF_MARK(2)
           if (!ok) break;
           tc_fence_after_sync();
           issue_pv(t, vslot, j > 0 ? 1u : 0u);
           if (j + 1 < n_of(t)) {
             if (!k_ready) {
-              ok = mbar_wait(bar_kv_full + 8 * kslot, (kidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+              ok = mbar_wait_warp(bar_kv_full + 8 * kslot, (kidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
               if (!ok) break;
               tc_fence_after_sync();
               k_ready = true;
             }
             issue_qk(t, kslot);
-            umma_commit(bar_s_full + 8 * t);
+            umma_commit_e<false>(bar_s_full + 8 * t, leader);
           } else {
-            umma_commit(bar_o_full + 8 * t);
+            umma_commit_e<false>(bar_o_full + 8 * t, leader);
           }
         }
         if (ok) {
-          umma_commit(bar_kv_empty + 8 * vslot);
-          if (j + 1 < n_kv) umma_commit(bar_kv_empty + 8 * kslot);
+          umma_commit_e<false>(bar_kv_empty + 8 * vslot, leader);
+          if (j + 1 < n_kv) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
         }
       }
       CFK_PROF_MARK(3)
-      CFK_PROF_FLUSH(8, 4, true)
+      CFK_PROF_FLUSH(8, 4, (leader != 0))
     }
    }
   } else {
@@ -292,7 +292,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       CFK_PROF_MARK(3)
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar_p_full + 8 * t);
+      mbar_arrive_warp(bar_p_full + 8 * t);
       CFK_PROF_MARK(4)
     }
     CFK_PROF_MARK(7)

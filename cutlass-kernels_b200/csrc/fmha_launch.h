@@ -11,6 +11,8 @@ namespace cfk {
 
 struct FmhaLaunch {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
+  CUtensorMap tm_k_half, tm_v_half;   // CTA-pair kernel: boxes of 64 keys x all columns / 128 keys x one 64-column span
+  int pair;                           // run the CTA-pair kernel (16-bit inputs, head dimension 128)
   FmhaParams p;
   int iterations;
   int exp_emu;   // 0..3: share (in quarters) of the exponentials computed on the FMA pipe
@@ -24,6 +26,8 @@ int fmha_launch_f16_f16_128(const FmhaLaunch&);
 int fmha_launch_bf16_bf16_64(const FmhaLaunch&);
 int fmha_launch_bf16_bf16_128(const FmhaLaunch&);
 int fmha_launch_e4m3_e4m3_128(const FmhaLaunch&);
+int fmha_launch_pair_f16(const FmhaLaunch&);
+int fmha_launch_pair_bf16(const FmhaLaunch&);
 
 int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L);
 

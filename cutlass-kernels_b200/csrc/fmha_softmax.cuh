@@ -140,7 +140,6 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
       tmem_wait_st();
     }
   }
-  CFK_PROF_MARK(2)
   const float negm = CFG::PSHIFT - m_ref * sl;
   const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);

@@ -165,3 +165,62 @@ def test_fmha_large_logits_trigger_rescale(lib, oracle, cuda):
     # the output alone is 1.95e-3: the bound here is 2e-3 plus that rounding step
     check(oracle, got, stats, f32, 1.0 / math.sqrt(D), False, 0, max_abs=4e-3)
 
+
+
+# ---- the CTA-pair kernel (CFK_TUNE_FMHA_CTA_PAIR): 16-bit inputs, head dimension 128 ----------------------
+
+@pytest.fixture
+def pair_lib(lib):
+    from cfk_b200 import TUNE_FMHA_CTA_PAIR
+    lib.set_tunable(TUNE_FMHA_CTA_PAIR, 1)
+    yield lib
+    lib.set_tunable(TUNE_FMHA_CTA_PAIR, -1)
+
+
+PAIR_CASES = [
+    (0, 1, 128, 128, 1, False),      # one key tile: only the first softmax warpgroup has work
+    (0, 1, 256, 256, 1, False),
+    (0, 2, 1024, 1024, 3, False),
+    (0, 1, 1024, 1024, 2, True),
+    (0, 1, 384, 640, 2, True),       # offset diagonal, odd tile count, second CTA of a pair beyond Sq
+    (0, 1, 1, 129, 1, False),        # a single query row
+    (0, 1, 333, 333, 1, True),
+    (0, 1, 200, 333, 2, False),
+    (1, 1, 2048, 2048, 2, True),     # bf16: two-term P in the first blocks, plain P after
+    (1, 2, 1536, 1536, 3, False),
+]
+
+
+@pytest.mark.parametrize("dtype,B,Sq,Skv,H,causal", PAIR_CASES)
+def test_fmha_pair_matches_oracle(pair_lib, oracle, cuda, dtype, B, Sq, Skv, H, causal):
+    low, f32, scales = make_qkv(dtype, B, Sq, Skv, H, 128, seed=4081 + Sq)
+    got, stats = run_fmha(pair_lib, low, scales, dtype, causal)
+    check(oracle, got, stats, f32, 1.0 / math.sqrt(128), causal, dtype)
+
+
+def test_fmha_pair_large_logits_trigger_rescale(pair_lib, oracle, cuda):
+    """Growing key norms move the running maximum past the lazy threshold again and again; in the pair kernel
+    that maximum is handed back and forth between the two softmax warpgroups that share a row."""
+    B, S, H, D = 1, 2048, 2, 128
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(B, S, H, D, generator=g)
+    k = torch.randn(B, S, H, D, generator=g) * torch.linspace(0.2, 6.0, S).view(1, S, 1, 1)
+    v = torch.randn(B, S, H, D, generator=g)
+    low = [x.half() for x in (q, k, v)]
+    f32 = [x.float().numpy() for x in low]
+    for causal in (False, True):
+        got, stats = run_fmha(pair_lib, low, [1, 1, 1], 0, causal)
+        check(oracle, got, stats, f32, 1.0 / math.sqrt(D), causal, 0, max_abs=4e-3)
+
+
+def test_fmha_pair_agrees_with_single_cta_kernel(lib, cuda):
+    from cfk_b200 import TUNE_FMHA_CTA_PAIR
+    low, _, scales = make_qkv(0, 2, 1024, 1024, 4, 128, seed=5)
+    o1, s1 = run_fmha(lib, low, scales, 0, True)
+    lib.set_tunable(TUNE_FMHA_CTA_PAIR, 1)
+    try:
+        o2, s2 = run_fmha(lib, low, scales, 0, True)
+    finally:
+        lib.set_tunable(TUNE_FMHA_CTA_PAIR, -1)
+    assert np.abs(o1 - o2).max() <= 1e-3
+    assert np.abs(s1["lse"] - s2["lse"]).max() <= 1e-4
