@@ -23,7 +23,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
            "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_set_tunable", "cfk_get_tunable"]
 
-TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_CTA_PAIR = 0, 1, 2
+TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL = 0, 1, 2
 
 
 class FmhaArgs(C.Structure):

@@ -173,7 +173,7 @@ extern "C" int cfk_set_tunable(int which, int value) {
   if (value < 0) value = kTunableDefault[which];
   if (which == CFK_TUNE_FMHA_EXP_EMU && value > 3) return CFK_ERR_INVALID_ARG;
   if (which == CFK_TUNE_FMHA_GROUP_MB && (value < 1 || value > 1024)) return CFK_ERR_INVALID_ARG;
-  if (which == CFK_TUNE_FMHA_CTA_PAIR && value > 1) return CFK_ERR_INVALID_ARG;
+  if (which == CFK_TUNE_FMHA_KERNEL && value > 1) return CFK_ERR_INVALID_ARG;
   g_tunable[which].store(value);
   return CFK_OK;
 }
@@ -279,8 +279,9 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
     return rc;
 
-  L.pair = (a->dtype != CFK_E4M3 && a->head_dim == 128 && g_tunable[CFK_TUNE_FMHA_CTA_PAIR].load() != 0) ? 1 : 0;
-  if (L.pair) {   // CTA-pair kernel: each CTA loads 64 keys of a K tile and one 64-column span of a V tile
+  L.variant = g_tunable[CFK_TUNE_FMHA_KERNEL].load();
+  if (L.variant == 1 && (a->dtype == CFK_E4M3 || a->head_dim != 128)) L.variant = 0;
+  if (L.variant == 1) {   // CTA-pair kernel: each CTA loads 64 keys of a K tile and one 64-column span of a V tile
     if ((rc = encode_bshd(&L.tm_k_half, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 64)))
       return rc;
     if ((rc = encode_bshd(&L.tm_v_half, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, 1)))

@@ -6,7 +6,7 @@
 namespace cfk {
 
 int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L) {
-  if (L.pair && head_dim == 128 && dtype == p_dtype && (dtype == CFK_FP16 || dtype == CFK_BF16))
+  if (L.variant == 1 && head_dim == 128 && dtype == p_dtype && (dtype == CFK_FP16 || dtype == CFK_BF16))
     return dtype == CFK_FP16 ? fmha_launch_pair_f16(L) : fmha_launch_pair_bf16(L);
   if (dtype == CFK_FP16 && p_dtype == CFK_FP16)
     return head_dim == 64 ? fmha_launch_f16_f16_64(L) : fmha_launch_f16_f16_128(L);

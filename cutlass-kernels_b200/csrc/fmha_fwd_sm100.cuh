@@ -49,8 +49,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_kv_full = sBar + 8;                   // [NSLOT]
   const uint32_t bar_kv_empty = bar_kv_full + 8 * C::NSLOT;  // [NSLOT]
   const uint32_t bar_s_full = bar_kv_empty + 8 * C::NSLOT;   // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;               // [2]
-  const uint32_t bar_o_full = bar_p_full + 16;               // [2]
+  const uint32_t bar_p_full = bar_s_full + 16;               // [2][2]: per tile, P of keys 0-63 / of keys 64-127
+  const uint32_t bar_o_full = bar_p_full + 32;               // [2]
   const uint32_t bar_o_staged = bar_o_full + 16;             // [2]
   const uint32_t off_misc = (bar_o_staged + 16) - sBar;
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
@@ -107,7 +107,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1);
-      mbar_init(bar_p_full + 8 * t, 4);
+      mbar_init(bar_p_full + 16 * t, 4);
+      mbar_init(bar_p_full + 16 * t + 8, 4);
       mbar_init(bar_o_full + 8 * t, 1);
       mbar_init(bar_o_staged + 8 * t, 128);
     }
@@ -183,15 +184,23 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                      leader);
         }
       };
-      auto issue_pv = [&](int t, int slot, uint32_t accumulate) {
+      // half 0: keys 0-63 of the tile, half 1: keys 64-127
+      auto issue_pv_half = [&](int t, int slot, int half, uint32_t accumulate) {
         const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
         const uint32_t a = tmem_base + t * 128;
 #pragma unroll
-        for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
+        for (int k2 = 0; k2 < C::PV_KSTEPS / 2; ++k2) {
+          const int kk = half * (C::PV_KSTEPS / 2) + k2;
           umma_ts_e<C::KIND8, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
-                                     kk > 0 ? 1u : accumulate, leader);
-        if (split) {   // second term of P lives in the upper half of the S_t columns
+                                     k2 > 0 ? 1u : accumulate, leader);
+        }
+      };
+      auto issue_pv_lo = [&](int t, int slot) {
+        const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
+        const uint32_t d = tmem_base + C::O_COL0 + t * HD;
+        const uint32_t a = tmem_base + t * 128;
+        {   // second term of P lives in the upper half of the S_t columns
 #pragma unroll
           for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
             umma_ts_e<C::KIND8, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
@@ -221,11 +230,24 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_of(t)) continue;
           CFK_PROF_MARK(3)
-          ok = mbar_wait_warp(bar_p_full + 8 * t, j & 1, actx, kErrFmhaPFull);
+          // with the two-term P the first-half barrier is not signalled; everything waits for the second
+          if (!split) {
+            ok = mbar_wait_warp(bar_p_full + 16 * t, j & 1, actx, kErrFmhaPFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
+          }
+          ok = mbar_wait_warp(bar_p_full + 16 * t + 8, j & 1, actx, kErrFmhaPFull);
           CFK_PROF_MARK(2)
           if (!ok) break;
           tc_fence_after_sync();
-          issue_pv(t, vslot, j > 0 ? 1u : 0u);
+          if (split) {
+            issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
+            issue_pv_half(t, vslot, 1, 1u);
+            issue_pv_lo(t, vslot);
+          } else {
+            issue_pv_half(t, vslot, 1, 1u);
+          }
           if (j + 1 < n_of(t)) {
             if (!k_ready) {
               ok = mbar_wait_warp(bar_kv_full + 8 * kslot, (kidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
@@ -287,12 +309,12 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }
         softmax_step<C, PT, HD, EMU>(sreg, tS, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim, lim - j * C::BN, split,
-                                     m_ref, m_true, l);
+                                     bar_p_full + 16 * t, m_ref, m_true, l);
       }
       CFK_PROF_MARK(3)
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive_warp(bar_p_full + 8 * t);
+      mbar_arrive_warp(bar_p_full + 16 * t + 8);
       CFK_PROF_MARK(4)
     }
     CFK_PROF_MARK(7)

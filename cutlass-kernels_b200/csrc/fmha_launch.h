@@ -12,7 +12,7 @@ namespace cfk {
 struct FmhaLaunch {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   CUtensorMap tm_k_half, tm_v_half;   // CTA-pair kernel: boxes of 64 keys x all columns / 128 keys x one 64-column span
-  int pair;                           // run the CTA-pair kernel (16-bit inputs, head dimension 128)
+  int variant;                        // 0 one CTA per 256 query rows, 1 CTA pairs (see cfk_b200.h)
   FmhaParams p;
   int iterations;
   int exp_emu;   // 0..3: share (in quarters) of the exponentials computed on the FMA pipe

@@ -91,10 +91,12 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
 // the row's raw scores (S_t, fp32 bits); on exit P has been written over S_t in tensor memory (tcgen05.st
 // issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first key tile of the row;
 // `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible column.
+// `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory (the UMMA
+// thread starts P V on those while the second half is still being computed); not used with the two-term P.
 template <class CFG, int PT, int HD, int EMU>
 __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tO, float sl, bool first,
-                                       bool mask_tile, int lim, bool split, float& m_ref, float& m_true,
-                                       float& l) {
+                                       bool mask_tile, int lim, bool split, uint32_t bar_half, float& m_ref,
+                                       float& m_true, float& l) {
   // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
   // needs it at all depends only on the tile, so the test costs no vote.
   if (mask_tile) {   // lim: last visible local column of this row
@@ -154,6 +156,13 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
                                               __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
       pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
       if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
+    }
+    if constexpr (!SPLIT) {
+      if (c == 2) {   // the stores of chunks 0 and 1 have had the time of this chunk's exponentials to land
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive_warp(bar_half);
+      }
     }
     if constexpr (CFG::PESZ == 2) {
       uint32_t hi[16], lo[16];

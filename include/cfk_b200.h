@@ -152,10 +152,11 @@ const char* cfk_last_cuda_error(void);
  *                           with a cubic on the FMA pipe instead of the special-function unit.
  *   CFK_TUNE_FMHA_GROUP_MB  causal only: heads are scheduled in groups whose K and V total at most
  *                           this many MiB (so they share L2), heaviest query blocks first.
- *   CFK_TUNE_FMHA_CTA_PAIR  0/1: 16-bit inputs with head dimension 128 run on pairs of CTAs (two SMs per 256
- *                           query rows, tcgen05 cta_group::2) instead of one CTA per 256 rows.
+ *   CFK_TUNE_FMHA_KERNEL    which FMHA kernel runs: 0 one CTA per 256 query rows (two 128-row tiles side by side);
+ *                           1 pairs of CTAs (two SMs per 256 rows, tcgen05 cta_group::2; 16-bit inputs with head
+ *                           dimension 128 only, other shapes run kernel 0).
  */
-enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_FMHA_CTA_PAIR = 2, CFK_TUNE_COUNT = 3 };
+enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_FMHA_KERNEL = 2, CFK_TUNE_COUNT = 3 };
 int cfk_set_tunable(int which, int value);
 int cfk_get_tunable(int which); /* -1 for an unknown knob */
 

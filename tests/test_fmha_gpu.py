@@ -167,14 +167,14 @@ def test_fmha_large_logits_trigger_rescale(lib, oracle, cuda):
 
 
 
-# ---- the CTA-pair kernel (CFK_TUNE_FMHA_CTA_PAIR): 16-bit inputs, head dimension 128 ----------------------
+# ---- the CTA-pair kernel (CFK_TUNE_FMHA_KERNEL): 16-bit inputs, head dimension 128 ----------------------
 
 @pytest.fixture
 def pair_lib(lib):
-    from cfk_b200 import TUNE_FMHA_CTA_PAIR
-    lib.set_tunable(TUNE_FMHA_CTA_PAIR, 1)
+    from cfk_b200 import TUNE_FMHA_KERNEL
+    lib.set_tunable(TUNE_FMHA_KERNEL, 1)
     yield lib
-    lib.set_tunable(TUNE_FMHA_CTA_PAIR, -1)
+    lib.set_tunable(TUNE_FMHA_KERNEL, -1)
 
 
 PAIR_CASES = [
@@ -214,13 +214,13 @@ def test_fmha_pair_large_logits_trigger_rescale(pair_lib, oracle, cuda):
 
 
 def test_fmha_pair_agrees_with_single_cta_kernel(lib, cuda):
-    from cfk_b200 import TUNE_FMHA_CTA_PAIR
+    from cfk_b200 import TUNE_FMHA_KERNEL
     low, _, scales = make_qkv(0, 2, 1024, 1024, 4, 128, seed=5)
     o1, s1 = run_fmha(lib, low, scales, 0, True)
-    lib.set_tunable(TUNE_FMHA_CTA_PAIR, 1)
+    lib.set_tunable(TUNE_FMHA_KERNEL, 1)
     try:
         o2, s2 = run_fmha(lib, low, scales, 0, True)
     finally:
-        lib.set_tunable(TUNE_FMHA_CTA_PAIR, -1)
+        lib.set_tunable(TUNE_FMHA_KERNEL, -1)
     assert np.abs(o1 - o2).max() <= 1e-3
     assert np.abs(s1["lse"] - s2["lse"]).max() <= 1e-4
