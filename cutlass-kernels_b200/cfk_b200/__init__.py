@@ -46,6 +46,7 @@ class GemmArgs(C.Structure):
         ("dtype", C.c_int), ("m", C.c_int), ("n", C.c_int), ("k", C.c_int), ("l", C.c_int),
         ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
         ("alpha", C.c_float), ("beta", C.c_float), ("c_row_major", C.c_int), ("iterations", C.c_int),
+        ("c_src", C.c_void_p),
     ]
 
 
@@ -117,17 +118,17 @@ class CfkLib:
             raise CfkError(rc, self.last_error())
 
     def gemm(self, a, b, c, *, dtype, m, n, k, l=1, alpha=1.0, beta=0.0, c_row_major=False, iterations=1,
-             stream=None) -> None:
+             c_src=None, stream=None) -> None:
         g = GemmArgs()
         g.dtype, g.m, g.n, g.k, g.l = dtype, m, n, k, l
-        g.a, g.b, g.c = _ptr(a), _ptr(b), _ptr(c)
+        g.a, g.b, g.c, g.c_src = _ptr(a), _ptr(b), _ptr(c), _ptr(c_src)
         g.alpha, g.beta, g.c_row_major, g.iterations = alpha, beta, int(bool(c_row_major)), iterations
         rc = self.gemm_raw(g, stream)
         if rc:
             raise CfkError(rc, self.last_error())
 
     def fill(self, dst, dtype, n, seed, kind="normal", scale=1.0, value=0.0, first_index=0, stream=None) -> None:
-        kinds = {"normal": 0, "uniform": 1, "const": 2}
+        kinds = {"normal": 0, "uniform": 1, "const": 2, "integers": 3}
         rc = int(self.lib.cfk_fill(_ptr(dst), dtype, n, seed, first_index, kinds[kind], scale, value, stream))
         if rc:
             raise CfkError(rc, self.last_error())

@@ -145,8 +145,9 @@ __global__ void fill_kernel(void* dst, int dtype, int64_t n, uint64_t seed, int6
       const uint64_t r = mix64(key ^ (uint64_t)(first + i));
       const float u1 = unit_open((uint32_t)r), u2 = unit_open((uint32_t)(r >> 32));
       v = (kind == 0) ? sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2) : 2.0f * u1 - 1.0f;
+      if (kind == 3) v = rintf(v * scale);   // integers in [-scale, scale]
     }
-    store_as(dst, dtype, i, v * scale);
+    store_as(dst, dtype, i, kind == 3 ? v : v * scale);
   }
 }
 
@@ -200,7 +201,7 @@ extern "C" int cfk_device_status(int* code_out) {
 
 extern "C" int cfk_fill(void* dst, int dtype, int64_t n, uint64_t seed, int64_t first_index, int kind, float scale,
                         float value, cfk_stream_t stream) {
-  if (!dst || n < 0 || !valid_dtype(dtype) || kind < 0 || kind > 2) return CFK_ERR_INVALID_ARG;
+  if (!dst || n < 0 || !valid_dtype(dtype) || kind < 0 || kind > 3) return CFK_ERR_INVALID_ARG;
   if (n == 0) return CFK_OK;
   const int threads = 256;
   const int64_t want = (n + threads - 1) / threads;

@@ -165,7 +165,8 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
       }
     }
     if constexpr (CFG::PESZ == 2) {
-      uint32_t hi[16], lo[16];
+      uint32_t hi[16];
+      [[maybe_unused]] uint32_t lo[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if constexpr (PT == kDtBF16) {

@@ -35,6 +35,7 @@ struct GemmParams {
   int64_t ldd;           // leading dimension of D (elements)
   int64_t d_batch;       // elements between consecutive D matrices
   void* d;
+  const void* src;       // matrix of the beta term (same layout as D); D itself when the update is in place
   float alpha, beta;
   int bf16;
   int tiles_r, tiles_c;  // 256 x 256 tiles
@@ -176,6 +177,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
       const int row = tr * C::TILE + row_in_tile;
       const int col0 = tc * C::TILE;
       uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+      const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.src) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
 #pragma unroll 1
       for (int c = 0; c < C::TILE / 32; ++c) {
         uint32_t acc[32];
@@ -191,7 +193,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
               for (int i = 0; i < 8; ++i) v[i] = p.alpha * __uint_as_float(acc[g * 8 + i]);
               uint4* dst = reinterpret_cast<uint4*>(drow + c * 32 + g * 8);
               if (p.beta != 0.f) {
-                const uint4 old = *dst;
+                const uint4 old = *reinterpret_cast<const uint4*>(srow + c * 32 + g * 8);
                 const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -244,7 +246,7 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->l <= 0 || a->iterations < 0) return CFK_ERR_INVALID_ARG;
   if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16) return CFK_ERR_UNSUPPORTED;
   if ((a->m % 8) || (a->n % 8) || (a->k % 8)) return CFK_ERR_UNSUPPORTED;
-  if (((uintptr_t)a->a | (uintptr_t)a->b | (uintptr_t)a->c) & 15u) return CFK_ERR_INVALID_ARG;
+  if (((uintptr_t)a->a | (uintptr_t)a->b | (uintptr_t)a->c | (uintptr_t)a->c_src) & 15u) return CFK_ERR_INVALID_ARG;
 
   int err = CFK_OK;
   int* status = device_status_block(&err);
@@ -274,6 +276,7 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   p.ldd = Cn;
   p.d_batch = (int64_t)R * Cn;
   p.d = a->c;
+  p.src = a->c_src ? a->c_src : a->c;
   p.alpha = a->alpha; p.beta = a->beta;
   p.bf16 = a->dtype == CFK_BF16;
   p.tiles_r = (R + GemmCfg::TILE - 1) / GemmCfg::TILE;

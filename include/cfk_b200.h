@@ -118,6 +118,8 @@ typedef struct cfk_gemm_args {
   float alpha, beta;
   int c_row_major; /* 0: column-major (reference), 1: row-major */
   int iterations;
+  const void* c_src; /* optional: when non-null the beta term reads this matrix (layout of c) and c is only written,
+                        D = alpha A B + beta C with separate C and D (src/cutlass-gemm/gemm.cu:316-323) */
 } cfk_gemm_args;
 
 int cfk_gemm(const cfk_gemm_args* args, cfk_stream_t stream);
@@ -126,7 +128,8 @@ int cfk_gemm(const cfk_gemm_args* args, cfk_stream_t stream);
  * Device-side random fills, element i depends only on (seed, first_index + i).
  * Replaces cfk::initialize_rand / initialize_const (include/utils/random.hpp:20-50).
  * kind 0: N(0,1); kind 1: U[-1,1]; kind 2: constant `value`.  The result is value * scale
- * rounded to `dtype`.
+ * rounded to `dtype`.  kind 3: integers, U[-1,1] * scale rounded to nearest (the integer-valued operands of
+ * src/cutlass-gemm/gemm.cu:268-293).
  */
 int cfk_fill(void* dst, int dtype, int64_t n, uint64_t seed, int64_t first_index, int kind, float scale,
              float value, cfk_stream_t stream);

@@ -64,3 +64,37 @@ def test_gemm_linearity_at_full_size(lib, cuda):
     for m, nn in idx.tolist():
         ref = float(a[m].double() @ b[nn].double())
         assert abs(float(c1[nn, m]) - ref) <= 2.0 ** -10 * max(1.0, abs(ref)) + 2e-3   # column-major C
+
+
+def test_gemm_separate_source_matrix_and_integer_operands(lib, oracle, cuda):
+    """D = alpha A B + beta C with C read-only and D written elsewhere, on the integer-valued operands of the
+    reference's CUTLASS-library GEMM program (src/cutlass-gemm/gemm.cu:268-323): sums of products of small integers
+    are exact in fp32, so every output that fp16 can hold must match the float64 result bit for bit."""
+    M, N, K = 384, 256, 512
+    a = torch.empty(M, K, dtype=torch.float16, device="cuda")
+    b = torch.empty(N, K, dtype=torch.float16, device="cuda")
+    c = torch.empty(N, M, dtype=torch.float16, device="cuda")       # column-major M x N
+    d = torch.full((N, M), -7.0, dtype=torch.float16, device="cuda")
+    for t, seed in ((a, 2024), (b, 2023), (c, 2022)):
+        lib.fill(t, 0, t.numel(), seed, kind="integers", scale=8.0)
+    assert float(a.float().abs().max()) == 8.0 and bool((a.float() == a.float().round()).all())
+    c_before = c.clone()
+    lib.gemm(a, b, d, dtype=0, m=M, n=N, k=K, alpha=1.0, beta=2.0, c_src=c)
+    lib.check_device()
+    assert torch.equal(c, c_before)                                  # the source matrix is not written
+    ref = a.double().cpu() @ b.double().cpu().T + 2.0 * c.double().cpu().T
+    want = ref.to(torch.float16)                                     # one rounding of the exact value
+    assert torch.equal(d.cpu().T.contiguous(), want.contiguous())
+
+
+def test_cutlass_gemm_cli_reports_passed(cuda):
+    """The driver with the reference's flags and result lines (src/cutlass-gemm/gemm.cu:182-243, 362-419)."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "cutlass-kernels_b200", "bin",
+                       "cutlass_gemm")
+    out = subprocess.run([exe, "--m=512", "--n=384", "--k=256", "--alpha=2", "--beta=0.5", "--iterations=3"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "Disposition: Passed" in out.stdout
+    assert "Problem Size: 512x384x256" in out.stdout and "GFLOPS:" in out.stdout
