@@ -245,7 +245,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return CFK_ERR_INVALID_ARG;
   if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_E4M3) return CFK_ERR_INVALID_ARG;
   if (a->out_dtype != CFK_FP16 && a->out_dtype != CFK_BF16) return CFK_ERR_INVALID_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
+  if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return CFK_ERR_UNSUPPORTED;
   if (a->dtype == CFK_E4M3 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
   if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
   if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;
@@ -273,9 +273,11 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   int rc;
   if ((rc = encode_bshd(&L.tm_q, a->dtype, a->q, a->batch, a->seqlen_q, a->heads, a->head_dim, qs[0], qs[1], qs[2], 128)))
     return rc;
-  if ((rc = encode_bshd(&L.tm_k, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 128)))
+  // head dimension 256: K and V tiles travel as two halves of 128 columns (two 128-byte spans) each
+  const int kv_spans = a->head_dim == 256 ? 2 : 0;
+  if ((rc = encode_bshd(&L.tm_k, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 128, kv_spans)))
     return rc;
-  if ((rc = encode_bshd(&L.tm_v, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128)))
+  if ((rc = encode_bshd(&L.tm_v, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, kv_spans)))
     return rc;
   if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
     return rc;
@@ -293,7 +295,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   p.B = a->batch; p.H = a->heads; p.Sq = a->seqlen_q; p.Skv = a->seqlen_kv;
   p.causal = a->causal ? 1 : 0;
   p.out_bf16 = a->out_dtype == CFK_BF16;
-  p.nqblk = (a->seqlen_q + 255) / 256;
+  p.nqblk = a->head_dim == 256 ? (a->seqlen_q + 127) / 128 : (a->seqlen_q + 255) / 256;   // hd 256: one tile per CTA
   p.split_keys = a->dtype == CFK_BF16 ? (a->p_split_keys < 0 ? 1024 : a->p_split_keys) : 0;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f * qd * kd;
   p.out_scale = vd;

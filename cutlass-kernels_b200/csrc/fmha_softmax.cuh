@@ -87,6 +87,68 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
 #define CFK_PROF_FLUSH(base, n, cond)
 #endif
 
+// Row maximum of the 128 scores a thread holds: sixteen independent chains, then a tree.
+__device__ __forceinline__ float row_max128(const uint32_t (&sreg)[128]) {
+  float mx[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) mx[i] = __uint_as_float(sreg[i]);
+#pragma unroll
+  for (int i = 16; i < 128; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
+#pragma unroll
+  for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+    for (int i = 0; i < w; ++i) mx[i] = fmaxf(mx[i], mx[i + w]);
+  return mx[0];
+}
+
+// P = 2^(s * sl + negm) for the 128 scores of a row, rounded to the operand type and stored to tensor memory at
+// tP (64 columns); with SPLIT (bf16) the rounding remainder goes to tLo as a second bf16 term.  Returns the row sum.
+template <int PT, int EMU, bool SPLIT>
+__device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t tP, uint32_t tLo, float sl, float negm) {
+  const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
+  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    float2 pr[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
+                                              __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
+      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+      if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
+    }
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if constexpr (PT == kDtBF16) {
+        hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
+        if constexpr (SPLIT)
+          lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
+      } else {
+        hi[j] = pack_f16x2(pr[j].x, pr[j].y);
+      }
+    }
+    tmem_st_x16(tP + 16 * c, hi);
+    if constexpr (SPLIT) tmem_st_x16(tLo + 16 * c, lo);
+  }
+  return (acc0.x + acc0.y) + (acc1.x + acc1.y);
+}
+
+// O row (fp32, `HD` columns at tO) *= alpha, in chunks of 32 columns.
+template <int HD>
+__device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {
+  uint32_t oreg[32];
+#pragma unroll 1
+  for (int c = 0; c < HD / 32; ++c) {
+    tmem_ld_x32(tO + c * 32, oreg);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+    tmem_st_x32(tO + c * 32, oreg);
+  }
+  tmem_wait_st();
+}
+
 // One key tile of the online softmax for the thread that owns a query row.  On entry sreg[0..127] holds
 // the row's raw scores (S_t, fp32 bits); on exit P has been written over S_t in tensor memory (tcgen05.st
 // issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first key tile of the row;

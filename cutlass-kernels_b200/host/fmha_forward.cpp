@@ -204,18 +204,22 @@ static int run(const Options& o, int dtype) {
 int main(int argc, char** argv) {
   const Options o = parse(argc, argv);
   if (o.help) {
-    std::printf("fmha_forward --batch-size=<int> --dim-size=<int> --head-size=<64|128> --seq-length=<int>\n"
+    std::printf("fmha_forward --batch-size=<int> --dim-size=<int> --head-size=<64|128|256> --seq-length=<int>\n"
                 "             --iterations=<int> --prec-type=<1 fp16|2 e4m3|3 bf16> --num-cuda-streams=<int>\n"
                 "             --reference-check=<bool> --causal=<bool> --check-heads=<int> --seed=<int>\n");
     return 0;
   }
-  if (o.head != 64 && o.head != 128) {
-    std::printf("head size %d is not supported (64 or 128)\n", o.head);   // the reference exits here too, :758-760
+  if (o.head != 64 && o.head != 128 && o.head != 256) {
+    std::printf("head size %d is not supported (64, 128 or 256)\n", o.head);   // the reference exits here too, :758-760
     return 1;
   }
   if (o.dim % o.head) { std::printf("dim-size must be a multiple of head-size\n"); return 1; }
-  if (o.prec == 1) return o.head == 64 ? run<__half, 64>(o, CFK_FP16) : run<__half, 128>(o, CFK_FP16);
-  if (o.prec == 3) return o.head == 64 ? run<__nv_bfloat16, 64>(o, CFK_BF16) : run<__nv_bfloat16, 128>(o, CFK_BF16);
+  if (o.prec == 1)
+    return o.head == 64 ? run<__half, 64>(o, CFK_FP16) : o.head == 128 ? run<__half, 128>(o, CFK_FP16) : run<__half, 256>(o, CFK_FP16);
+  if (o.prec == 3)
+    return o.head == 64    ? run<__nv_bfloat16, 64>(o, CFK_BF16)
+           : o.head == 128 ? run<__nv_bfloat16, 128>(o, CFK_BF16)
+                           : run<__nv_bfloat16, 256>(o, CFK_BF16);
   if (o.prec == 2) {
     if (o.head != 128) { std::printf("e4m3 needs head-size 128\n"); return 1; }
     return run<e4m3_t, 128>(o, CFK_E4M3);

@@ -52,6 +52,12 @@ CASES = [
     (1, 1, 512, 512, 2, 64, True),
     (2, 1, 1024, 1024, 2, 128, False),
     (2, 1, 1024, 1024, 2, 128, True),
+    (0, 1, 128, 128, 1, 256, False),     # head dimension 256: one query tile per CTA, one key tile
+    (0, 2, 1024, 1024, 2, 256, False),
+    (0, 1, 1024, 1024, 2, 256, True),
+    (1, 1, 2048, 2048, 1, 256, True),    # bf16: two-term P in the first blocks
+    (1, 1, 384, 640, 2, 256, True),
+    (0, 1, 333, 200, 1, 256, False),     # ragged lengths
 ]
 
 
@@ -150,10 +156,12 @@ def test_fmha_scale_is_linear_in_v_and_rows_sum_to_one(lib, cuda):
     assert np.abs(o2 - 2 * o1).max() <= 1e-3
 
 
-def test_fmha_large_logits_trigger_rescale(lib, oracle, cuda):
+@pytest.mark.parametrize("D", [128, 256])
+def test_fmha_large_logits_trigger_rescale(lib, oracle, cuda, D):
     """Keys whose scores grow along the sequence force the running maximum to move past the lazy
-    threshold many times, so the O-rescale path is exercised."""
-    B, S, H, D = 1, 2048, 1, 128
+    threshold many times, so the O-rescale path is exercised (at head dimension 256 that path also
+    waits for the previous P V, which is still in flight there)."""
+    B, S, H = 1, 2048, 1
     g = torch.Generator().manual_seed(0)
     q = torch.randn(B, S, H, D, generator=g)
     k = torch.randn(B, S, H, D, generator=g) * torch.linspace(0.2, 6.0, S).view(1, S, 1, 1)
