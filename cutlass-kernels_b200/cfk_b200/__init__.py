@@ -38,6 +38,7 @@ class FmhaArgs(C.Structure):
         ("softmax_scale", C.c_float), ("causal", C.c_int),
         ("q_descale", C.c_float), ("k_descale", C.c_float), ("v_descale", C.c_float),
         ("iterations", C.c_int),
+        ("s_dump", C.c_void_p),
     ]
 
 
@@ -97,7 +98,8 @@ class CfkLib:
     def fmha_args(self, q, k, v, o, *, dtype, batch, heads, seqlen_q, seqlen_kv, head_dim, softmax_scale,
                   causal=False, out_dtype=FP16, p_split_keys=-1, lse=None, mi=None, sprime=None,
                   q_descale=1.0, k_descale=1.0, v_descale=1.0, iterations=1,
-                  q_stride=(0, 0, 0), k_stride=(0, 0, 0), v_stride=(0, 0, 0), o_stride=(0, 0, 0)) -> FmhaArgs:
+                  q_stride=(0, 0, 0), k_stride=(0, 0, 0), v_stride=(0, 0, 0), o_stride=(0, 0, 0),
+                  s_dump=None) -> FmhaArgs:
         a = FmhaArgs()
         a.dtype, a.out_dtype, a.p_split_keys = dtype, out_dtype, p_split_keys
         a.batch, a.heads, a.seqlen_q, a.seqlen_kv, a.head_dim = batch, heads, seqlen_q, seqlen_kv, head_dim
@@ -110,6 +112,7 @@ class CfkLib:
         a.softmax_scale, a.causal = softmax_scale, int(bool(causal))
         a.q_descale, a.k_descale, a.v_descale = q_descale, k_descale, v_descale
         a.iterations = iterations
+        a.s_dump = _ptr(s_dump)
         return a
 
     def fmha_forward(self, *pos, stream=None, **kw) -> None:

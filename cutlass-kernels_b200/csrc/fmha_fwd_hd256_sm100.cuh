@@ -257,6 +257,7 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_ld_x32(tS + 96, sreg + 96);
       tmem_wait_ld();
 
+      if (p.s_dump) dump_scores(p, sreg, 128, batch, head, row_g, j * C::BN);
       if (j * C::BN + 127 > tile_min_lim) {   // this tile has masked columns for some row
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }

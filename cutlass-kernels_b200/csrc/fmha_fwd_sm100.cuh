@@ -304,6 +304,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_ld();
       CFK_PROF_MARK(1)
 
+      if (p.s_dump) dump_scores(p, sreg, 128, batch, head, row_g, j * C::BN);
       // mask, row maximum, lazy rescale of O and l, P = 2^(x - m) written over S_t, row sum
       {
         int lim = p.Skv - 1;

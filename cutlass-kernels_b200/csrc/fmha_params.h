@@ -21,6 +21,8 @@ struct FmhaParams {
   float* lse;        // optional [B][H][Sq]: natural-log sum of exp of the scaled scores
   float* mi;         // optional [B][H][Sq]: row maximum in the log2 domain
   float* sprime;     // optional [B][H][Sq]: sum of 2^(x - mi), not inverted
+  void* s_dump;      // optional debug output [B][H][Sq][Skv]: raw Q K^T (16-bit); see cfk_b200.h
+  int s_dump_bf16;   // element type of s_dump: 0 fp16, 1 bf16
   int* status;       // device status word
 };
 

@@ -134,6 +134,21 @@ __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t
   return (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
 
+// Debugging only: the `n` raw scores of query row `row_g` against keys key0 .. key0+n-1 (held by the calling thread,
+// before scale and mask) go to S[b][h][row][key], rounded to fp16 / bf16.  The reference writes the same tile from its
+// GEMM-I accumulator fragment (fmha_consumer.h:31-42).
+__device__ __forceinline__ void dump_scores(const FmhaParams& p, const uint32_t* sreg, int n, int batch, int head,
+                                            int row_g, int key0) {
+  if (row_g >= p.Sq) return;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(p.s_dump) + (((size_t)batch * p.H + head) * p.Sq + row_g) * (size_t)p.Skv;
+  for (int i = 0; i < n; ++i) {
+    const int key = key0 + i;
+    if (key >= p.Skv) break;
+    const float v = __uint_as_float(sreg[i]);
+    dst[key] = p.s_dump_bf16 ? (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu) : (uint16_t)(pack_f16x2(v, 0.f) & 0xffffu);
+  }
+}
+
 // O row (fp32, `HD` columns at tO) *= alpha, in chunks of 32 columns.
 template <int HD>
 __device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {

@@ -145,6 +145,7 @@ extern "C" int cfk_fmha_forward_static(const cfk_fmha_args* a, cfk_stream_t stre
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f * qd * kd;
   p.out_scale = vd;
   p.lse = a->lse; p.mi = a->mi; p.sprime = a->sprime;
+  p.s_dump = a->s_dump; p.s_dump_bf16 = a->dtype == CFK_BF16;
   p.status = status;
   L.iterations = a->iterations;
   L.stream = st;

@@ -27,7 +27,7 @@ struct e4m3_t { unsigned char bits; };   // 1-byte element: cfk::dtype_of falls 
 
 struct Options {
   int batch = 4, dim = 2048, head = 64, seq = 4096, iterations = 20, prec = 2, streams = 1, check_heads = 2;
-  bool check = false, causal = false, help = false;
+  bool check = false, causal = false, help = false, verify_all = false;
   unsigned long long seed = 3080;
 };
 
@@ -55,6 +55,7 @@ static Options parse(int argc, char** argv) {
     else if (flag(argv[i], "seed", &v)) o.seed = std::strtoull(v.c_str(), nullptr, 10);
     else if (flag(argv[i], "reference-check", &v)) o.check = (v == "true" || v == "1");
     else if (flag(argv[i], "causal", &v)) o.causal = (v == "true" || v == "1");
+    else if (flag(argv[i], "verify-all", &v)) o.verify_all = o.check = (v == "true" || v == "1");
     else std::fprintf(stderr, "ignoring unknown argument %s\n", argv[i]);
   }
   return o;
@@ -71,9 +72,17 @@ static Options parse(int argc, char** argv) {
 
 // Host attention on float inputs for one (batch 0, head h): the reference's unfused recipe
 // (include/utils/fmha_cutlass.hpp:275-314) with an optional lower-triangular mask.
+// Optional extras for the verify-all run: raw (unscaled, unmasked) scores of the visible keys, row maxima of the
+// scaled scores (natural-log domain) and inverse row sums, the three things the reference's COPYOUTMM0 / COPYOUTMI
+// builds compare (src/fmha-pipeline/fmha_forward.cu:640-672).
 static void host_attention_head(const std::vector<float>& q, const std::vector<float>& k, const std::vector<float>& v,
-                                int S, int H, int D, int h, float scale, bool causal, std::vector<float>* out) {
+                                int S, int H, int D, int h, float scale, bool causal, std::vector<float>* out,
+                                std::vector<float>* raw = nullptr, std::vector<float>* row_max = nullptr,
+                                std::vector<float>* inv_sum = nullptr) {
   out->assign((size_t)S * D, 0.f);
+  if (raw) raw->assign((size_t)S * S, 0.f);
+  if (row_max) row_max->assign(S, 0.f);
+  if (inv_sum) inv_sum->assign(S, 0.f);
 #pragma omp parallel
   {
     std::vector<float> sc(S);
@@ -87,11 +96,14 @@ static void host_attention_head(const std::vector<float>& q, const std::vector<f
         const float* kj = &k[((size_t)j * H + h) * D];
         for (int d = 0; d < D; ++d) acc += qi[d] * kj[d];
         sc[j] = acc * scale;
+        if (raw) (*raw)[(size_t)i * S + j] = acc;
         mx = std::fmax(mx, sc[j]);
       }
       float sum = 0.f;
       for (int j = 0; j < nv; ++j) { sc[j] = std::exp(sc[j] - mx); sum += sc[j]; }
       const float inv = 1.f / sum;
+      if (row_max) (*row_max)[i] = mx;
+      if (inv_sum) (*inv_sum)[i] = inv;
       float* o = &(*out)[(size_t)i * D];
       for (int j = 0; j < nv; ++j) {
         const float pj = sc[j] * inv;
@@ -176,11 +188,55 @@ static int run(const Options& o, int dtype) {
     if (cfk_convert(out, CFK_FP16, tmp, CFK_FP32, (int64_t)nb, 1.f, nullptr)) return 1;
     CUDA_OK(cudaMemcpy(ho.data(), tmp, nb * sizeof(float), cudaMemcpyDeviceToHost));
     cudaFree(tmp);
-    long long bad = 0, total = 0;
+    // verify-all: one more launch that also writes the raw scores (the S argument of the launcher)
+    const bool dump = o.verify_all && dtype != CFK_E4M3;
+    std::vector<float> hs, hmi, hsp;
+    if (o.verify_all) {
+      T* sdump = nullptr;
+      if (dump) {
+        CUDA_OK(cudaMalloc(&sdump, (size_t)B * H * S * S * sizeof(T)));
+        CUDA_OK(cudaMemset(sdump, 0, (size_t)B * H * S * S * sizeof(T)));
+        lo.dump_scores = true;
+        fmhaForwardDevice<T, T, float, __half, HEADDIM>(S, S, H, B, q, k, v, sdump, out, mi, sprime, 1, scale, 0);
+        lo.dump_scores = false;
+        CUDA_OK(cudaDeviceSynchronize());
+        if (cfk::last_status() != CFK_OK) return 1;
+        const size_t ns = (size_t)heads * S * S;   // batch 0, first heads
+        float* tmp2;
+        CUDA_OK(cudaMalloc(&tmp2, ns * sizeof(float)));
+        if (cfk_convert(sdump, dtype, tmp2, CFK_FP32, (int64_t)ns, 1.f, nullptr)) return 1;
+        hs.resize(ns);
+        CUDA_OK(cudaMemcpy(hs.data(), tmp2, ns * sizeof(float), cudaMemcpyDeviceToHost));
+        cudaFree(tmp2);
+        cudaFree(sdump);
+      }
+      hmi.resize((size_t)H * S);
+      hsp.resize((size_t)H * S);
+      CUDA_OK(cudaMemcpy(hmi.data(), mi, hmi.size() * sizeof(float), cudaMemcpyDeviceToHost));
+      CUDA_OK(cudaMemcpy(hsp.data(), sprime, hsp.size() * sizeof(float), cudaMemcpyDeviceToHost));
+    }
+    auto off = [](float got, float want) {   // the reference's element rule, include/utils/random.hpp:64-89
+      const float ad = std::fabs(got - want), rel = ad / std::fabs(want + 1e-5f);
+      return std::isnan(want) || std::isnan(ad) || std::isinf(ad) || (ad > 5e-3f && rel > 1e-1f);
+    };
+    long long bad = 0, total = 0, bad_s = 0, bad_max = 0, bad_sum = 0;
     double maxabs = 0;
     for (int h = 0; h < heads; ++h) {
-      std::vector<float> ref;
-      host_attention_head(hf[0], hf[1], hf[2], S, H, D, h, 1.f / std::sqrt((float)D), o.causal, &ref);
+      std::vector<float> ref, raw, rmax, rinv;
+      host_attention_head(hf[0], hf[1], hf[2], S, H, D, h, 1.f / std::sqrt((float)D), o.causal, &ref,
+                          dump ? &raw : nullptr, o.verify_all ? &rmax : nullptr, o.verify_all ? &rinv : nullptr);
+      if (o.verify_all) {
+        for (int i = 0; i < S; ++i) {
+          // mi is in the log2 domain and sprime is not inverted (fmha_forward.cu:655-672)
+          if (off(hmi[(size_t)h * S + i] * 0.69314718f, rmax[i])) ++bad_max;
+          if (off(1.f / hsp[(size_t)h * S + i], rinv[i])) ++bad_sum;
+          if (dump) {
+            const int nv = o.causal ? i + 1 : S;
+            for (int j = 0; j < nv; ++j)
+              if (off(hs[((size_t)h * S + i) * S + j], raw[(size_t)i * S + j])) ++bad_s;
+          }
+        }
+      }
       for (int i = 0; i < S; ++i)
         for (int d = 0; d < D; ++d) {
           const float got = ho[((size_t)i * H + h) * D + d], want = ref[(size_t)i * D + d];
@@ -191,11 +247,18 @@ static int run(const Options& o, int dtype) {
         }
     }
     const double pct = 100.0 * (double)bad / (double)total;
+    if (o.verify_all) {
+      if (dump) std::printf("gemm-check-1: %s\n", bad_s == 0 ? "Passed" : "Failed");
+      else std::printf("gemm-check-1: not run (scores are dumped for 16-bit inputs only)\n");
+      std::printf("max-check: %s\n", bad_max == 0 ? "Passed" : "Failed");
+      std::printf("sum-check: %s\n", bad_sum == 0 ? "Passed" : "Failed");
+      if (bad_s || bad_max || bad_sum) ret = 2;
+    }
     std::printf("Error (percentage) : %f\n", pct);
     std::printf("max abs diff %g over %d head(s) of batch 0\n", maxabs, heads);
     const double allowed = dtype == CFK_E4M3 ? 0.001 : 0.0001;   // fmha_forward.cu:638-639
     std::printf("gemm-check-2: %s\n", pct <= allowed ? "Passed" : "Failed");
-    ret = pct <= allowed ? 0 : 2;
+    if (pct > allowed) ret = 2;
   }
   cudaFree(q); cudaFree(k); cudaFree(v); cudaFree(out); cudaFree(mi); cudaFree(sprime);
   return ret;
@@ -206,7 +269,7 @@ int main(int argc, char** argv) {
   if (o.help) {
     std::printf("fmha_forward --batch-size=<int> --dim-size=<int> --head-size=<64|128|256> --seq-length=<int>\n"
                 "             --iterations=<int> --prec-type=<1 fp16|2 e4m3|3 bf16> --num-cuda-streams=<int>\n"
-                "             --reference-check=<bool> --causal=<bool> --check-heads=<int> --seed=<int>\n");
+                "             --reference-check=<bool> --verify-all=<bool> --causal=<bool> --check-heads=<int> --seed=<int>\n");
     return 0;
   }
   if (o.head != 64 && o.head != 128 && o.head != 256) {

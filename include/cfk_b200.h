@@ -75,6 +75,10 @@ typedef struct cfk_fmha_args {
   int causal;     /* key j visible to query i iff j <= i + (seqlen_kv - seqlen_q) */
   float q_descale, k_descale, v_descale; /* multiply the stored values to get real ones; use 1 for 16-bit */
   int iterations; /* number of back-to-back launches (the reference's loop, fmha_forward.cu:375-382) */
+  void* s_dump;   /* optional, debugging only: [batch][heads][seqlen_q][seqlen_kv], the reference's S of a COPYOUTMM0
+                     build (fmha_consumer.h:31-42): Q K^T before the softmax scale and before masking, rounded to the
+                     input type (fp16 for e4m3 inputs, in stored units).  Key tiles a causal mask skips are not
+                     written.  Slows the kernel down. */
 } cfk_fmha_args;
 
 int cfk_fmha_forward(const cfk_fmha_args* args, cfk_stream_t stream);

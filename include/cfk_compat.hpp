@@ -63,6 +63,7 @@ struct LaunchOptions {
   float* lse = nullptr;
   int out_dtype = CFK_FP16;
   int p_split_keys = -1;
+  bool dump_scores = false;   // write the S argument like a COPYOUTMM0 build of the reference (16-bit inputs only)
 };
 inline LaunchOptions& launch_options() {
   static thread_local LaunchOptions o;
@@ -78,7 +79,6 @@ void fmhaForwardDevice(int SEQLEN, int KEYLEN, int NUMHEADS, int BATCH, PrecType
   static_assert(std::is_same<SoftType, float>::value, "softmax statistics are fp32");
   static_assert(sizeof(OutputType) == 2, "the output is a 16-bit type");
   static_assert(sizeof(PrecType) == sizeof(Gemm2Type), "Q/K and V share one element type here");
-  (void)S;
   const cfk::LaunchOptions& opt = cfk::launch_options();
   cfk_fmha_args a{};
   a.dtype = cfk::dtype_of<PrecType>::value;
@@ -91,6 +91,7 @@ void fmhaForwardDevice(int SEQLEN, int KEYLEN, int NUMHEADS, int BATCH, PrecType
   a.causal = opt.causal ? 1 : 0;
   a.q_descale = opt.q_descale; a.k_descale = opt.k_descale; a.v_descale = opt.v_descale;
   a.iterations = iterations;
+  a.s_dump = (opt.dump_scores && sizeof(PrecType) == 2) ? S : nullptr;   // else S is ignored (may be nullptr)
   cfk::note_status("fmhaForwardDevice", cfk_fmha_forward(&a, stream));
 }
 

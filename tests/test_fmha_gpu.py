@@ -232,3 +232,36 @@ def test_fmha_pair_agrees_with_single_cta_kernel(lib, cuda):
         lib.set_tunable(TUNE_FMHA_KERNEL, -1)
     assert np.abs(o1 - o2).max() <= 1e-3
     assert np.abs(s1["lse"] - s2["lse"]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("dtype,D,causal,kernel", [(0, 128, False, 0), (1, 128, True, 0), (0, 64, True, 0),
+                                                   (0, 128, True, 1), (0, 256, False, 0)])
+def test_fmha_score_dump_is_raw_q_k_transposed(lib, cuda, dtype, D, causal, kernel):
+    """The debugging output of a COPYOUTMM0 build of the reference (fmha_consumer.h:31-42): Q K^T before scale and
+    mask, rounded to the input type, [B][H][Sq][Skv]; key tiles that a causal mask skips stay untouched."""
+    from cfk_b200 import TUNE_FMHA_KERNEL
+    B, Sq, Skv, H = 1, 300, 424, 2
+    low, f32, scales = make_qkv(dtype, B, Sq, Skv, H, D, seed=11)
+    q, k, v = (x.cuda() for x in low)
+    o = torch.empty(B, Sq, H, D, device="cuda", dtype=torch.float16)
+    dump = torch.full((B, H, Sq, Skv), -77.0, device="cuda", dtype=q.dtype)
+    lib.set_tunable(TUNE_FMHA_KERNEL, kernel)
+    try:
+        lib.fmha_forward(q, k, v, o, dtype=dtype, batch=B, heads=H, seqlen_q=Sq, seqlen_kv=Skv, head_dim=D,
+                         softmax_scale=1.0 / math.sqrt(D), causal=causal, s_dump=dump)
+        lib.check_device()
+    finally:
+        lib.set_tunable(TUNE_FMHA_KERNEL, -1)
+    ref = np.einsum("bihd,bjhd->bhij", f32[0].astype(np.float64), f32[1].astype(np.float64))
+    got = dump.float().cpu().numpy()
+    written = got != -77.0
+    # every key a row may see is inside a written tile; with a causal mask whole 128-key tiles beyond the
+    # last row of the CTA's query block are skipped
+    i = np.arange(Sq)[:, None]
+    j = np.arange(Skv)[None, :]
+    visible = (j <= i + (Skv - Sq)) if causal else np.ones((Sq, Skv), bool)
+    assert written[0, 0][visible].all()
+    if causal:
+        assert not written[0, 0][0, 256:].any()      # row 0 sees keys 0..124; tiles from key 256 on are never computed
+    tol = np.abs(ref) * 2.0 ** (-10 if dtype == 0 else -7) + 1e-3
+    assert (np.abs(got - ref)[written] <= tol[written]).all()
