@@ -246,7 +246,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_E4M3) return CFK_ERR_INVALID_ARG;
   if (a->out_dtype != CFK_FP16 && a->out_dtype != CFK_BF16) return CFK_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return CFK_ERR_UNSUPPORTED;
-  if (a->dtype == CFK_E4M3 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
+  if (a->dtype == CFK_E4M3 && a->head_dim == 64) return CFK_ERR_UNSUPPORTED;   // 64-byte rows: not built
   if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
   if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;
   const int pdt = a->dtype;   // P is rounded to the input type
@@ -274,7 +274,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if ((rc = encode_bshd(&L.tm_q, a->dtype, a->q, a->batch, a->seqlen_q, a->heads, a->head_dim, qs[0], qs[1], qs[2], 128)))
     return rc;
   // head dimension 256: K and V tiles travel as two halves of 128 columns (two 128-byte spans) each
-  const int kv_spans = a->head_dim == 256 ? 2 : 0;
+  const int kv_spans = a->head_dim == 256 ? esz : 0;   // 128 columns = esz spans of 128 bytes
   if ((rc = encode_bshd(&L.tm_k, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 128, kv_spans)))
     return rc;
   if ((rc = encode_bshd(&L.tm_v, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, kv_spans)))

@@ -9,6 +9,7 @@ int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L) {
   if (head_dim == 256) {
     if (dtype == CFK_FP16 && p_dtype == CFK_FP16) return fmha_launch_hd256_f16(L);
     if (dtype == CFK_BF16 && p_dtype == CFK_BF16) return fmha_launch_hd256_bf16(L);
+    if (dtype == CFK_E4M3 && p_dtype == CFK_E4M3) return fmha_launch_hd256_e4m3(L);
     return CFK_ERR_UNSUPPORTED;
   }
   if (L.variant == 1 && head_dim == 128 && dtype == p_dtype && (dtype == CFK_FP16 || dtype == CFK_BF16))

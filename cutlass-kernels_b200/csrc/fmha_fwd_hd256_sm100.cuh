@@ -1,4 +1,5 @@
-// Flash-attention forward for sm_100a, head dimension 256, 16-bit inputs: one CTA per (128 query rows, head, batch).
+// Flash-attention forward for sm_100a, head dimension 256 (fp16, bf16 or e4m3 inputs): one CTA per (128 query rows,
+// head, batch).
 //
 // The reference runs head dimension 256 through the same kernels as 64 and 128 with a smaller key tile
 // (src/fmha-pipeline/fmha_forward.cu:746-757, compile_run_all_config.sh:3-6).  On B200 the O accumulator of one
@@ -13,8 +14,9 @@
 // 128x128x16-per-half) against about 1700 clocks of softmax for the tile, so a single softmax warpgroup keeps the
 // tensor core busy: while P_j V_j and Q K_{j+2}^T run on buffer A, the warpgroup is already working on S_B(j+1).
 //   warps 0-3  softmax (thread r owns row r) and epilogue      warp 4  UMMA issue      warp 5  TMA producer
-// Shared memory: Q tile 64 KB (later the staged O tile) and a ring of five 32 KB slots; K_j and V_j each travel
-// as two [128 keys][128 columns] halves (K halves split the reduction of Q K^T, V halves the columns of O).
+// Shared memory: 64 KB for the Q tile and later the staged O tile, and a ring of 32 KB slots (16 KB for e4m3); K_j and
+// V_j each travel as two [128 keys][128 columns] halves (K halves split the reduction of Q K^T, V halves the columns
+// of O).  With e4m3 inputs the tensor core runs at twice the rate and the single softmax warpgroup is the bound.
 #pragma once
 #include "fmha_softmax.cuh"
 
@@ -24,28 +26,33 @@ constexpr int kErrFmhaPvDone256 = 111;
 
 template <int DT>
 struct FmhaHd256Cfg {
-  static_assert(DT == kDtF16 || DT == kDtBF16, "16-bit inputs only");
   static constexpr int HD = 256, BN = 128;
-  static constexpr int SUBB = 128 * 128;              // one 64-column span of a 128-row tile
-  static constexpr int QTILEB = 4 * SUBB;             // Q tile and staged O tile: 64 KB
-  static constexpr int SLOTB = 2 * SUBB;              // half a K or V tile: 128 keys x 128 columns
+  static constexpr int ESZ = (DT == kDtE4M3) ? 1 : 2;
+  static constexpr bool KIND8 = (ESZ == 1);
+  static constexpr int SUBB = 128 * 128;              // one 128-byte span of a 128-row tile
+  static constexpr int HSPANS = ESZ;                  // spans per half of a K or V tile (128 columns)
+  static constexpr int QB = 2 * HSPANS * SUBB;        // bytes of the Q tile
+  static constexpr int QTILEB = 4 * SUBB;             // Q tile, later the staged O tile (16-bit, 64 KB)
+  static constexpr int SLOTB = HSPANS * SUBB;         // half a K or V tile: 128 keys x 128 columns
+  static constexpr int HALF_KSTEPS = 128 * ESZ / 32;  // UMMAs per half tile (32 bytes of reduction each)
   static constexpr int SMEM_LIMIT = 232448;
   static constexpr int BARB = 512;
-  static constexpr int NSLOT = (SMEM_LIMIT - 1024 - BARB - QTILEB) / SLOTB;   // 5
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - 1024 - BARB - QTILEB) / SLOTB;   // 5 (16-bit) or 10
+  static constexpr int NSLOT = NSLOT_FIT > 10 ? 10 : NSLOT_FIT;
   static_assert(NSLOT >= 4, "ring too small");
   static constexpr int SMEM_BYTES = 1024 + QTILEB + NSLOT * SLOTB + BARB;
-  static constexpr int V_STEPB = 16 * 128;            // bytes between successive groups of 16 keys of a V half
+  static constexpr int V_STEPB = (32 / ESZ) * 128;    // bytes between the key groups of successive UMMAs in a V half
   static constexpr int TMEM_COLS = 512, O_COL0 = 256;
-  static constexpr uint32_t FMT = (DT == kDtBF16) ? kFmtBF16 : kFmtF16;
+  static constexpr uint32_t FMT = (DT == kDtBF16) ? kFmtBF16 : 0u;   // f16 and e4m3 are both code 0 of their kind
   static constexpr uint32_t IDESC_QK = make_idesc(1, FMT, FMT, 0, 0, 128, 128);
   static constexpr uint32_t IDESC_PV = make_idesc(1, FMT, FMT, 0, 1, 128, 128);
   static constexpr int NTHREADS = 192;
-  static constexpr float TAU = 8.0f;
-  static constexpr float PSHIFT = 0.0f;
+  static constexpr float TAU = (DT == kDtE4M3) ? 2.0f : 8.0f;
+  static constexpr float PSHIFT = (DT == kDtE4M3) ? 6.0f : 0.0f;
 };
 
-// tm_q / tm_o: boxes of 128 rows x all four 64-column spans; tm_k / tm_v: 128 keys x two spans.
-template <int DT, int EMU>
+// tm_q / tm_o: boxes of 128 rows x all 128-byte spans of a row; tm_k / tm_v: 128 keys x 128 columns (HSPANS spans).
+template <int DT, int EMU, bool DUMP = false>
 __global__ void __launch_bounds__(192, 1)
 fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -146,7 +153,7 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // =========================== TMA producer ===========================
     // Ring order = order of use: K_0 (two halves), K_1, then for every j: V_j (two halves), K_{j+2}.
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar_q_full, C::QTILEB);
+      mbar_arrive_expect_tx(bar_q_full, C::QB);
       tma_load_5d(sQ, &tm_q, bar_q_full, 0, row0, 0, head, batch);
       int idx = 0;
       auto load = [&](const CUtensorMap* tm, int j) -> bool {   // both halves of K_j or V_j
@@ -155,7 +162,7 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           const uint32_t ph = (idx / C::NSLOT) & 1;
           if (!mbar_wait(bar_kv_empty + 8 * slot, ph ^ 1u, actx, kErrFmhaKvEmpty)) return false;
           mbar_arrive_expect_tx(bar_kv_full + 8 * slot, C::SLOTB);
-          tma_load_5d(sRing + slot * C::SLOTB, tm, bar_kv_full + 8 * slot, 0, j * C::BN, 2 * h, head, batch);
+          tma_load_5d(sRing + slot * C::SLOTB, tm, bar_kv_full + 8 * slot, 0, j * C::BN, C::HSPANS * h, head, batch);
         }
         return true;
       };
@@ -184,12 +191,12 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int h = 0; h < 2; ++h, ++idx) {
         if (!slot_wait()) return false;
         tc_fence_after_sync();
-        const uint64_t a0 = desc_advance_lo(aq0, h * 2 * C::SUBB);
+        const uint64_t a0 = desc_advance_lo(aq0, h * C::SLOTB);
         const uint64_t b0 = desc_advance_lo(bk0, (idx % C::NSLOT) * C::SLOTB);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < C::HALF_KSTEPS; ++kk) {
           const uint32_t off = (kk >> 2) * C::SUBB + (kk & 3) * 32;
-          umma_ss_e<false, false>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK,
+          umma_ss_e<C::KIND8, false>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK,
                                   (h > 0 || kk > 0) ? 1u : 0u, leader);
         }
         umma_commit_e<false>(bar_kv_empty + 8 * (idx % C::NSLOT), leader);
@@ -206,13 +213,13 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const uint32_t d = tmem_base + C::O_COL0 + h * 128;
         const uint64_t b0 = desc_advance_lo(bv0, (idx % C::NSLOT) * C::SLOTB);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_ts_e<false, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
+        for (int kk = 0; kk < C::HALF_KSTEPS; ++kk)
+          umma_ts_e<C::KIND8, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
                                   kk > 0 ? 1u : accumulate, leader);
         if (split) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts_e<false, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
+          for (int kk = 0; kk < C::HALF_KSTEPS; ++kk)
+            umma_ts_e<C::KIND8, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
         }
         umma_commit_e<false>(bar_kv_empty + 8 * (idx % C::NSLOT), leader);
       }
@@ -257,7 +264,7 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_ld_x32(tS + 96, sreg + 96);
       tmem_wait_ld();
 
-      if (p.s_dump) dump_scores(p, sreg, 128, batch, head, row_g, j * C::BN);
+      if constexpr (DUMP) dump_scores(p, sreg, batch, head, row_g, j * C::BN);
       if (j * C::BN + 127 > tile_min_lim) {   // this tile has masked columns for some row
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }

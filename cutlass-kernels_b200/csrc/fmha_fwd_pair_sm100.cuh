@@ -59,7 +59,7 @@ struct FmhaPairCfg {
 };
 
 // tm_q / tm_o: boxes of 128 rows x all columns; tm_k: 64 keys x all columns; tm_v: 128 keys x one 64-column span.
-template <int DT, int EMU>
+template <int DT, int EMU, bool DUMP = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
 fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -339,7 +339,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_arrive_cluster_warp(leader_s_free);     // S_X may be overwritten by Q K_{j+2}^T
       CFK_PROF_MARK(1)
 
-      if (p.s_dump && j < tiles_for(row0)) dump_scores(p, sreg, 128, batch, head, row_g, j * C::BN);   // not the peer's extra tile
+      if (DUMP && j < tiles_for(row0)) dump_scores(p, sreg, batch, head, row_g, j * C::BN);   // not the peer's extra tile
       if (j * C::BN + 127 > tile_min_lim) {   // this tile has masked columns for some row of the CTA
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }

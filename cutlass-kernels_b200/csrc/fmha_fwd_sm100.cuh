@@ -28,8 +28,9 @@
 
 namespace cfk {
 
-// EMU: of every four pairs of probabilities, how many are computed on the FMA pipe (0..3).
-template <int DT, int PT, int HD, int EMU>
+// EMU: of every four pairs of probabilities, how many are computed on the FMA pipe (0..3).  DUMP: the debugging
+// build that also writes the raw scores (FmhaParams::s_dump); a separate instantiation keeps the test out of the loop.
+template <int DT, int PT, int HD, int EMU, bool DUMP = false>
 __global__ void __launch_bounds__(384, 1)
 fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -304,7 +305,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_wait_ld();
       CFK_PROF_MARK(1)
 
-      if (p.s_dump) dump_scores(p, sreg, 128, batch, head, row_g, j * C::BN);
+      if constexpr (DUMP) dump_scores(p, sreg, batch, head, row_g, j * C::BN);
       // mask, row maximum, lazy rescale of O and l, P = 2^(x - m) written over S_t, row sum
       {
         int lim = p.Skv - 1;

@@ -6,10 +6,10 @@
 
 namespace cfk {
 
-template <int DT, int PT, int HD, int EMU>
+template <int DT, int PT, int HD, int EMU, bool DUMP = false>
 int fmha_launch_e(const FmhaLaunch& L) {
   using C = FmhaCfg<DT, PT, HD>;
-  auto kern = fmha_fwd_kernel<DT, PT, HD, EMU>;
+  auto kern = fmha_fwd_kernel<DT, PT, HD, EMU, DUMP>;
   static thread_local int attr_set_for_device = -1;
   int dev = 0;
   if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess) return CFK_ERR_NO_DRIVER;
@@ -28,6 +28,7 @@ int fmha_launch_e(const FmhaLaunch& L) {
 
 template <int DT, int PT, int HD>
 int fmha_launch_t(const FmhaLaunch& L) {
+  if (L.p.s_dump) return fmha_launch_e<DT, PT, HD, 0, true>(L);   // debugging build: raw scores are written too
   switch (L.exp_emu) {
     case 0: return fmha_launch_e<DT, PT, HD, 0>(L);
     case 1: return fmha_launch_e<DT, PT, HD, 1>(L);

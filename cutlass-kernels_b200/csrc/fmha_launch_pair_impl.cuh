@@ -6,10 +6,10 @@
 
 namespace cfk {
 
-template <int DT, int EMU>
+template <int DT, int EMU, bool DUMP = false>
 int fmha_launch_pair_e(const FmhaLaunch& L) {
   using C = FmhaPairCfg<DT>;
-  auto kern = fmha_fwd_pair_kernel<DT, EMU>;
+  auto kern = fmha_fwd_pair_kernel<DT, EMU, DUMP>;
   static thread_local int attr_set_for_device = -1;
   int dev = 0;
   if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess) return CFK_ERR_NO_DRIVER;
@@ -29,6 +29,7 @@ int fmha_launch_pair_e(const FmhaLaunch& L) {
 
 template <int DT>
 int fmha_launch_pair_t(const FmhaLaunch& L) {
+  if (L.p.s_dump) return fmha_launch_pair_e<DT, 0, true>(L);   // debugging build: raw scores are written too
   switch (L.exp_emu) {
     case 0: return fmha_launch_pair_e<DT, 0>(L);
     case 1: return fmha_launch_pair_e<DT, 1>(L);

@@ -102,7 +102,8 @@ __device__ __forceinline__ float row_max128(const uint32_t (&sreg)[128]) {
 }
 
 // P = 2^(s * sl + negm) for the 128 scores of a row, rounded to the operand type and stored to tensor memory at
-// tP (64 columns); with SPLIT (bf16) the rounding remainder goes to tLo as a second bf16 term.  Returns the row sum.
+// tP (64 columns, 32 for e4m3); with SPLIT (bf16) the rounding remainder goes to tLo as a second bf16 term.  Returns
+// the row sum.
 template <int PT, int EMU, bool SPLIT>
 __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t tP, uint32_t tLo, float sl, float negm) {
   const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
@@ -117,19 +118,27 @@ __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t
       pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
       if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
     }
-    uint32_t hi[16], lo[16];
+    if constexpr (PT == kDtE4M3) {   // 32 probabilities = 8 words = 8 columns
+      uint32_t w[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if constexpr (PT == kDtBF16) {
-        hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
-        if constexpr (SPLIT)
-          lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
-      } else {
-        hi[j] = pack_f16x2(pr[j].x, pr[j].y);
+      for (int j = 0; j < 8; ++j) w[j] = pack_e4m3x4(pr[2 * j].x, pr[2 * j].y, pr[2 * j + 1].x, pr[2 * j + 1].y);
+      tmem_st_x8(tP + 8 * c, w);
+    } else {
+      uint32_t hi[16];
+      [[maybe_unused]] uint32_t lo[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if constexpr (PT == kDtBF16) {
+          hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
+          if constexpr (SPLIT)
+            lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
+        } else {
+          hi[j] = pack_f16x2(pr[j].x, pr[j].y);
+        }
       }
+      tmem_st_x16(tP + 16 * c, hi);
+      if constexpr (SPLIT) tmem_st_x16(tLo + 16 * c, lo);
     }
-    tmem_st_x16(tP + 16 * c, hi);
-    if constexpr (SPLIT) tmem_st_x16(tLo + 16 * c, lo);
   }
   return (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
@@ -137,15 +146,19 @@ __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t
 // Debugging only: the `n` raw scores of query row `row_g` against keys key0 .. key0+n-1 (held by the calling thread,
 // before scale and mask) go to S[b][h][row][key], rounded to fp16 / bf16.  The reference writes the same tile from its
 // GEMM-I accumulator fragment (fmha_consumer.h:31-42).
-__device__ __forceinline__ void dump_scores(const FmhaParams& p, const uint32_t* sreg, int n, int batch, int head,
+template <int N>
+__device__ __forceinline__ void dump_scores(const FmhaParams& p, const uint32_t (&sreg)[N], int batch, int head,
                                             int row_g, int key0) {
   if (row_g >= p.Sq) return;
-  uint16_t* dst = reinterpret_cast<uint16_t*>(p.s_dump) + (((size_t)batch * p.H + head) * p.Sq + row_g) * (size_t)p.Skv;
-  for (int i = 0; i < n; ++i) {
-    const int key = key0 + i;
-    if (key >= p.Skv) break;
-    const float v = __uint_as_float(sreg[i]);
-    dst[key] = p.s_dump_bf16 ? (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu) : (uint16_t)(pack_f16x2(v, 0.f) & 0xffffu);
+  uint16_t* dst = reinterpret_cast<uint16_t*>(p.s_dump) + (((size_t)batch * p.H + head) * p.Sq + row_g) * (size_t)p.Skv + key0;
+  const int left = p.Skv - key0;
+  // fully unrolled with constant indices: the score registers must not be addressed dynamically
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    if (i < left) {
+      const float v = __uint_as_float(sreg[i]);
+      dst[i] = p.s_dump_bf16 ? (uint16_t)(pack_bf16x2(v, 0.f) & 0xffffu) : (uint16_t)(pack_f16x2(v, 0.f) & 0xffffu);
+    }
   }
 }
 

@@ -18,8 +18,8 @@ if [[ ! -x "$BIN" ]]; then echo "build first: make -C $HERE/.."; exit 1; fi
 STATUS=0
 for PREC in "${PRECS[@]}"; do
 for HEAD in "${HEADSIZES[@]}"; do
-  if [[ $PREC == 2 && $HEAD != 128 ]]; then
-    echo "PREC=$PREC, HEAD=$HEAD: not built (e4m3 runs at head size 128 only)"
+  if [[ $PREC == 2 && $HEAD == 64 ]]; then
+    echo "PREC=$PREC, HEAD=$HEAD: not built (e4m3 needs rows of at least 128 bytes: head sizes 128 and 256)"
     continue
   fi
   if [[ $MODE == "verify" || $MODE == "verify-all" ]]; then
