@@ -74,7 +74,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 int encode_tiled(CUtensorMap* map, int dtype, int rank, const void* base, const uint64_t* dims,
-                 const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+                 const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return CFK_ERR_NO_DRIVER;
   CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -88,7 +88,8 @@ int encode_tiled(CUtensorMap* map, int dtype, int rank, const void* base, const 
   for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
   for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
   CUresult r = fn(map, dt, (cuuint32_t)rank, const_cast<void*>(base), gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     g_last_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
@@ -100,12 +101,13 @@ int encode_tiled(CUtensorMap* map, int dtype, int rank, const void* base, const 
 int encode_bshd(CUtensorMap* map, int dtype, const void* base, int batch, int seq, int heads, int d, int64_t sb,
                 int64_t ss, int64_t sh, int box_rows, int box_spans) {
   const int esz = dtype_size(dtype);
-  const uint64_t span = 128 / esz;                // elements per 128-byte span
-  const uint64_t nspan = (uint64_t)d * esz / 128;
+  const int span_bytes = d * esz < 128 ? d * esz : 128;   // rows shorter than 128 bytes (e4m3, d = 64) are one 64-byte span
+  const uint64_t span = (uint64_t)span_bytes / esz;       // elements per span
+  const uint64_t nspan = (uint64_t)d * esz / span_bytes;
   const uint64_t dims[5] = {span, (uint64_t)seq, nspan, (uint64_t)heads, (uint64_t)batch};
-  const uint64_t strides[4] = {(uint64_t)ss * esz, 128, (uint64_t)sh * esz, (uint64_t)sb * esz};
+  const uint64_t strides[4] = {(uint64_t)ss * esz, (uint64_t)span_bytes, (uint64_t)sh * esz, (uint64_t)sb * esz};
   const uint32_t box[5] = {(uint32_t)span, (uint32_t)box_rows, (uint32_t)(box_spans > 0 ? box_spans : (int)nspan), 1, 1};
-  return encode_tiled(map, dtype, 5, base, dims, strides, box, true);
+  return encode_tiled(map, dtype, 5, base, dims, strides, box, span_bytes);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -246,7 +248,6 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_E4M3) return CFK_ERR_INVALID_ARG;
   if (a->out_dtype != CFK_FP16 && a->out_dtype != CFK_BF16) return CFK_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return CFK_ERR_UNSUPPORTED;
-  if (a->dtype == CFK_E4M3 && a->head_dim == 64) return CFK_ERR_UNSUPPORTED;   // 64-byte rows: not built
   if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
   if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;
   const int pdt = a->dtype;   // P is rounded to the input type

@@ -171,16 +171,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // Descriptor words that do not change: Q_0 and Q_1 (K-major), and ring slot 0 seen as a K tile
       // (K-major) and as a V tile (MN-major: LBO = distance between the 64-element column groups, i.e. one
       // sub-tile; SBO = distance between groups of 8 keys).  A slot or a k-step adds a constant to the low word.
-      const uint64_t aq0 = make_smem_desc(sQ, 16, 1024, kSwizzle128B);
-      const uint64_t bk0 = make_smem_desc(sRing, 16, 1024, kSwizzle128B);
-      const uint64_t bv0 = make_smem_desc(sRing, C::SUBB, 1024, kSwizzle128B);
+      const uint64_t aq0 = make_smem_desc(sQ, 16, C::SBO, C::SWZ);
+      const uint64_t bk0 = make_smem_desc(sRing, 16, C::SBO, C::SWZ);
+      const uint64_t bv0 = make_smem_desc(sRing, C::SUBB, C::SBO, C::SWZ);
       auto issue_qk = [&](int t, int slot) {
         const uint64_t a0 = desc_advance_lo(aq0, t * C::TILEB);
         const uint64_t b0 = desc_advance_lo(bk0, slot * C::TILEB);
         const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int kk = 0; kk < C::QK_KSTEPS; ++kk) {
-          const uint32_t off = (kk >> 2) * C::SUBB + (kk & 3) * 32;
+          const uint32_t off = (kk / C::KSPS) * C::SUBB + (kk % C::KSPS) * 32;
           umma_ss_e<C::KIND8, false>(d, desc_advance_lo(a0, off), desc_advance_lo(b0, off), C::IDESC_QK, kk > 0 ? 1u : 0u,
                                      leader);
         }

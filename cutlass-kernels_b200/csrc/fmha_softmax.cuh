@@ -18,12 +18,17 @@ struct FmhaCfg {
   static constexpr bool KIND8 = (ESZ == 1);
   static constexpr int BM = 128, BN = 128;
   static constexpr int ROWB = HD * ESZ;            // bytes per row of a Q/K/V tile
-  static_assert(ROWB % 128 == 0, "rows must be whole 128-byte swizzle spans");
-  static constexpr int NSUB = ROWB / 128;          // 128-byte wide sub-tiles per tile
-  static constexpr int SUBB = 128 * 128;           // bytes per sub-tile (128 rows x 128 B)
+  static constexpr int SPANB = ROWB < 128 ? ROWB : 128;   // swizzle span: 128 bytes, or the whole 64-byte row (e4m3, d = 64)
+  static_assert(ROWB % SPANB == 0 && (SPANB == 128 || SPANB == 64), "rows must be whole swizzle spans");
+  static constexpr uint32_t SWZ = SPANB == 128 ? kSwizzle128B : kSwizzle64B;
+  static constexpr int SBO = 8 * SPANB;            // bytes between groups of 8 rows of a sub-tile
+  static constexpr int KSPS = SPANB / 32;          // UMMA k-steps (32 bytes of reduction) per span
+  static constexpr int NSUB = ROWB / SPANB;        // span-wide sub-tiles per tile
+  static constexpr int SUBB = 128 * SPANB;         // bytes per sub-tile (128 rows x one span)
   static constexpr int TILEB = NSUB * SUBB;        // bytes per Q/K/V tile
-  static constexpr int ONSUB = HD * 2 / 128;       // output is always 16 bit
-  static constexpr int OTILEB = ONSUB * SUBB;
+  static constexpr int ONSUB = HD * 2 / 128;       // output is always 16 bit, in 128-byte spans
+  static constexpr int OSUBB = 128 * 128;
+  static constexpr int OTILEB = ONSUB * OSUBB;
   static constexpr bool O_SEPARATE = (OTILEB > TILEB);  // else O is staged over the Q tile
   static constexpr int SMEM_LIMIT = 232448;
   static constexpr int FIXEDB = 2 * TILEB + (O_SEPARATE ? 2 * OTILEB : 0);
@@ -34,7 +39,7 @@ struct FmhaCfg {
   static constexpr int SMEM_BYTES = 1024 + FIXEDB + NSLOT * TILEB + BARB;
   static constexpr int QK_KSTEPS = ROWB / 32;      // each UMMA consumes 32 bytes of K extent
   static constexpr int PV_KSTEPS = BN * ESZ / 32;
-  static constexpr int V_STEPB = (32 / ESZ) * 128; // bytes between successive 32-byte-K groups of V rows
+  static constexpr int V_STEPB = (32 / ESZ) * SPANB;   // bytes between successive 32-byte-K groups of V rows
   static constexpr int PCOLS = BN * PESZ / 4;      // TMEM columns taken by P
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL0 = 256;
@@ -303,7 +308,7 @@ __device__ __forceinline__ void stage_output(uint32_t tO, uint32_t stage, int r,
       pk[i] = out_bf16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
     }
     // 32 output columns = 64 bytes = four 16-byte chunks of sub-tile c/2, 128-byte swizzled
-    const uint32_t row_addr = stage + (c >> 1) * CFG::SUBB + r * 128;
+    const uint32_t row_addr = stage + (c >> 1) * CFG::OSUBB + r * 128;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t chunk = (uint32_t)((c & 1) * 4 + i) ^ (uint32_t)(r & 7);

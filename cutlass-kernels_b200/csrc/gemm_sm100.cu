@@ -267,8 +267,8 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   const uint64_t ys[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)Cn};
   const uint32_t yb[3] = {GemmCfg::BK, GemmCfg::BNH, 1};      // per CTA: 128 rows of Y
   int rc;
-  if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, true))) return rc;
-  if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, true))) return rc;
+  if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, 128))) return rc;
+  if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, 128))) return rc;
 
   GemmParams p;
   std::memset(&p, 0, sizeof(p));

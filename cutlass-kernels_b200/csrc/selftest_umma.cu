@@ -131,14 +131,14 @@ extern "C" int cfk_selftest_umma(const void* a, const void* b, float* d, int n, 
     const uint64_t dims[3] = {(uint64_t)k, 128, 1};
     const uint64_t str[2] = {128, 128 * 128};
     const uint32_t box[3] = {(uint32_t)k, 128, 1};
-    int rc = encode_tiled(&tm_a, a_fmt, 3, a, dims, str, box, true);
+    int rc = encode_tiled(&tm_a, a_fmt, 3, a, dims, str, box, 128);
     if (rc) return rc;
   }
   if (!b_mn_major) {
     const uint64_t dims[3] = {(uint64_t)k, (uint64_t)n, 1};
     const uint64_t str[2] = {128, (uint64_t)128 * n};
     const uint32_t box[3] = {(uint32_t)k, (uint32_t)n, 1};
-    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, true);
+    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, 128);
     if (rc) return rc;
   } else {
     const uint64_t span = 128 / esz;                 // elements per 128-byte span of n
@@ -146,7 +146,7 @@ extern "C" int cfk_selftest_umma(const void* a, const void* b, float* d, int n, 
     const uint64_t dims[3] = {span, (uint64_t)k, nspan};
     const uint64_t str[2] = {(uint64_t)n * esz, 128};
     const uint32_t box[3] = {(uint32_t)span, (uint32_t)k, (uint32_t)nspan};
-    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, true);
+    int rc = encode_tiled(&tm_b, b_fmt, 3, b, dims, str, box, 128);
     if (rc) return rc;
   }
   SelfParams p;

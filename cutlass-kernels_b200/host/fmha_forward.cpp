@@ -284,8 +284,8 @@ int main(int argc, char** argv) {
            : o.head == 128 ? run<__nv_bfloat16, 128>(o, CFK_BF16)
                            : run<__nv_bfloat16, 256>(o, CFK_BF16);
   if (o.prec == 2) {
-    if (o.head == 64) { std::printf("e4m3 needs head-size 128 or 256 (rows of at least 128 bytes)\n"); return 1; }
-    return o.head == 128 ? run<e4m3_t, 128>(o, CFK_E4M3) : run<e4m3_t, 256>(o, CFK_E4M3);
+    return o.head == 64 ? run<e4m3_t, 64>(o, CFK_E4M3)
+           : o.head == 128 ? run<e4m3_t, 128>(o, CFK_E4M3) : run<e4m3_t, 256>(o, CFK_E4M3);
   }
   std::printf("unknown prec-type %d\n", o.prec);
   return 1;

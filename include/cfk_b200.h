@@ -49,7 +49,7 @@ enum cfk_status {
  * Tensors are [batch][seq][head][head_dim] with head_dim contiguous (the reference's layout,
  * fmha_forward.cu:151-152).  A stride of 0 means "packed".  Strides are in elements; every
  * stride times the element size must be a multiple of 16 bytes and every base pointer 16-byte
- * aligned.  head_dim must be 64, 128 or 256 (128 or 256 for e4m3).  Accumulation and softmax are fp32.
+ * aligned.  head_dim must be 64, 128 or 256.  Accumulation and softmax are fp32.
  */
 typedef struct cfk_fmha_args {
   int dtype;      /* cfk_dtype of Q, K and V: FP16, BF16 or E4M3 */

@@ -41,7 +41,7 @@ def _args(lib, **over):
 @pytest.mark.parametrize("over,code", [
     (dict(batch=0), 1), (dict(seqlen_q=-1), 1), (dict(softmax_scale=0.0), 1), (dict(softmax_scale=float("nan")), 1),
     (dict(dtype=cfk_b200.FP32), 1), (dict(out_dtype=cfk_b200.E4M3), 1),
-    (dict(head_dim=96), 2), (dict(dtype=cfk_b200.E4M3, head_dim=64), 2),
+    (dict(head_dim=96), 2), (dict(head_dim=512), 2),
     (dict(p_split_keys=-2), 1),
     (dict(causal=True, seqlen_q=256, seqlen_kv=128), 2),
     (dict(q=0x1008), 1), (dict(q_stride=(128 * 2 * 64, 2 * 64 + 3, 64)), 1),

@@ -58,6 +58,8 @@ CASES = [
     (1, 1, 2048, 2048, 1, 256, True),    # bf16: two-term P in the first blocks
     (1, 1, 384, 640, 2, 256, True),
     (0, 1, 333, 200, 1, 256, False),     # ragged lengths
+    (2, 1, 1024, 1024, 2, 64, False),    # e4m3 at head dimension 64: 64-byte rows, 64-byte swizzle
+    (2, 2, 333, 500, 3, 64, True),
     (2, 1, 1024, 1024, 2, 256, False),   # e4m3 at head dimension 256
     (2, 1, 640, 640, 1, 256, True),
 ]
