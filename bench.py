@@ -325,6 +325,25 @@ def main():
     # DRAM bytes (read + write) of one kernel launch on this workload, from one ncu capture of the CLI driver
     # on the same shape (profiles/fmha_fwd_*.md name the command); the algorithmic bytes are Q+K+V+O.
     traffic = NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload)
+    # Tensor-core ceiling of this run's own clocks: the library's dense-UMMA probe on the workload's operand type
+    # (one CTA per SM, operands resident in shared memory), a burst of a few ms and a sustained third of a second.
+    # For e4m3 it is the roofline denominator (no library GEMM figure exists); for 16-bit types it is reported
+    # beside the driver-measured cuBLAS figures.
+    def umma_probe(groups, reps):
+        lib.umma_peak(dt, 2000, stream=sptr)
+        torch.cuda.synchronize()
+        e0.record(stream)
+        fl = 0.0
+        for _ in range(reps):
+            fl += lib.umma_peak(dt, groups, stream=sptr)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return fl / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    umma_burst = umma_probe(20000, 1)
+    umma_sustained = umma_probe(100000, 10 if dt != 2 else 20)
+    lib.check_device()
+    if dt == 2:
+        burst, sustained, peak_kind = umma_burst, umma_sustained, "live cfk_umma_peak"
     line = {
         "metric": "fmha_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_max, "higher_is_better": True, "scaling": "weak",
@@ -333,7 +352,10 @@ def main():
                    "l2": "inputs (3 x %d MiB per GPU) exceed the 126 MB L2" % (q.numel() * q.element_size() >> 20),
                    "parallelism": "batch x head slices per GPU, no collective"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": burst, "unit": "TFLOP/s", "frac": per_gpu / burst,
-                     "traffic": traffic, "peak_source": f"{peak_kind} bf16 burst (timed region {ms * args.steps:.0f} ms)",
+                     "traffic": traffic,
+                     "peak_source": f"{peak_kind} {'e4m3 UMMA' if dt == 2 else 'bf16 GEMM'} burst (timed region {ms * args.steps:.0f} ms)",
+                     "umma_peak_live": {"dtype": DT_NAME[dt], "burst": umma_burst, "sustained": umma_sustained,
+                                        "what": "dense tcgen05.mma 128x256 from shared memory, all SMs, this run"},
                      "peak_sustained": sustained, "frac_sustained": per_gpu / sustained,
                      "nominal": NOMINAL[dt], "frac_nominal": per_gpu / NOMINAL[dt]},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

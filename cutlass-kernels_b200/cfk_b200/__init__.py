@@ -21,7 +21,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
                 6: "DEVICE_WAIT", 7: "TOO_LARGE"}
 
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
-           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_set_tunable", "cfk_get_tunable"]
+           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_set_tunable", "cfk_get_tunable"]
 
 TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL = 0, 1, 2
 
@@ -83,6 +83,7 @@ class CfkLib:
         L.cfk_device_status.argtypes = [C.POINTER(C.c_int)]
         L.cfk_last_cuda_error.restype = C.c_char_p
         L.cfk_selftest_umma.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 8 + [C.c_void_p]
+        L.cfk_umma_peak.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p]
 
     # -- raw calls (return the status code) ---------------------------------------------------
     def fmha_forward_raw(self, args: FmhaArgs, stream=None) -> int:
@@ -140,6 +141,14 @@ class CfkLib:
         rc = int(self.lib.cfk_convert(_ptr(src), src_dtype, _ptr(dst), dst_dtype, n, scale, stream))
         if rc:
             raise CfkError(rc, self.last_error())
+
+    def umma_peak(self, dtype, groups, stream=None) -> float:
+        """Enqueues the tensor-core ceiling probe; returns the floating-point operations of the launch."""
+        flops = C.c_double(0.0)
+        rc = int(self.lib.cfk_umma_peak(dtype, groups, C.byref(flops), stream))
+        if rc:
+            raise CfkError(rc, self.last_error())
+        return float(flops.value)
 
     def selftest_umma(self, a, b, d, n, a_fmt, b_fmt, b_mn_major, a_from_tmem, lbo=-1, sbo=-1, step=-1,
                       stream=None) -> int:

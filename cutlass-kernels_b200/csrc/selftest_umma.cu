@@ -109,6 +109,69 @@ selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
   }
 }
 
+
+// Dense-UMMA rate probe: every CTA (one per SM) issues `groups` x 4 UMMAs of 128 x 256 x (32 bytes of K) on
+// pseudo-random operands that never leave shared memory, alternating two accumulators.  Nothing but the tensor core
+// and its shared-memory operand reads is exercised, so flops / time is the ceiling a kernel of this family can see
+// at the clock the run settles on (the fp8 figure has no vendor-library counterpart to take from a GEMM).
+constexpr int kErrPeakDone = 303;
+
+template <bool KIND8>
+__global__ void __launch_bounds__(128, 1) umma_peak_kernel(int groups, uint32_t idesc, uint32_t seed, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA = smem_base;             // 128 rows x 128 B
+  const uint32_t sB = smem_base + 16384;     // 256 rows x 128 B
+  const uint32_t sBar = sB + 32768;
+  volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(smem_gen + (sBar - smem_base) + 16);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(smem_gen + (sBar - smem_base) + 20);
+  const AbortCtx actx{s_abort, status};
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (cta_should_skip(status)) return;
+  // finite pseudo-random operands: e4m3 bytes with exponent 0..7 / bf16 halves in [1, 2) with random sign
+  uint32_t* words = reinterpret_cast<uint32_t*>(smem_gen);
+  for (int i = tid; i < (16384 + 32768) / 4; i += 128) {
+    uint32_t h = (uint32_t)i * 2654435761u ^ seed ^ (blockIdx.x * 40503u);
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    words[i] = KIND8 ? (h & 0xbfbfbfbfu) : ((h & 0x807f807fu) | 0x3f803f80u);
+  }
+  if (tid == 0) {
+    mbar_init(sBar, 1);
+    *s_abort = 0u;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 512);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *s_tmem_base;
+  if (warp == 1) {   // warp-uniform issue loop, one elected lane executes the instructions
+    const uint32_t leader = elect_one();
+    const uint64_t a0 = make_smem_desc(sA, 16, 1024, kSwizzle128B);
+    const uint64_t b0 = make_smem_desc(sB, 16, 1024, kSwizzle128B);
+    for (int g = 0; g < groups; ++g) {
+      const uint32_t d = tmem_base + (g & 1) * 256;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_ss_e<KIND8, false>(d, desc_advance_lo(a0, kk * 32), desc_advance_lo(b0, kk * 32), idesc, (g > 1 || kk > 0) ? 1u : 0u,
+                                leader);
+    }
+    umma_commit_e<false>(sBar, leader);
+    (void)mbar_wait_warp(sBar, 0, actx, kErrPeakDone);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace cfk
 
 using namespace cfk;
@@ -178,4 +241,28 @@ extern "C" int cfk_selftest_umma(const void* a, const void* b, float* d, int n, 
   }
   selftest_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(tm_a, tm_b, p);
   return note_cuda(cudaGetLastError(), "selftest launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+}
+
+extern "C" int cfk_umma_peak(int dtype, int groups, double* flops_out, cfk_stream_t stream) {
+  if (groups < 1 || groups > (1 << 24) || !flops_out) return CFK_ERR_INVALID_ARG;
+  if (dtype != CFK_FP16 && dtype != CFK_BF16 && dtype != CFK_E4M3) return CFK_ERR_UNSUPPORTED;
+  int err = CFK_OK;
+  int* status = device_status_block(&err);
+  if (!status) return err;
+  int dev = 0, sms = 0;
+  if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess) return CFK_ERR_NO_DRIVER;
+  if (note_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "sm count") != cudaSuccess)
+    return CFK_ERR_LAUNCH;
+  const bool k8 = dtype == CFK_E4M3;
+  const uint32_t fmt = dtype == CFK_BF16 ? kFmtBF16 : 0u;
+  const uint32_t idesc = make_idesc(1, fmt, fmt, 0, 0, 128, 256);
+  const int smem = 1024 + 16384 + 32768 + 64;
+  auto kern = k8 ? umma_peak_kernel<true> : umma_peak_kernel<false>;
+  if (note_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute(peak)") !=
+      cudaSuccess)
+    return CFK_ERR_LAUNCH;
+  kern<<<sms, 128, smem, (cudaStream_t)stream>>>(groups, idesc, 12345u, status);
+  // per UMMA: 2 * 128 * 256 * (32 bytes of K / element size) flops
+  *flops_out = (double)sms * groups * 4.0 * 2.0 * 128 * 256 * (32 / dtype_size(dtype));
+  return note_cuda(cudaGetLastError(), "umma peak launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
 }

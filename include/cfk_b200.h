@@ -171,6 +171,15 @@ int cfk_get_tunable(int which); /* -1 for an unknown knob */
 int cfk_version(void);
 
 /*
+ * Tensor-core ceiling probe: one CTA per SM issues `groups` x 4 tcgen05.mma 128 x 256 x (32 bytes of K) on random
+ * operands resident in shared memory; *flops_out receives the floating-point operations of the launch, so that the
+ * caller, timing the stream, gets the dense UMMA rate of `dtype` (FP16, BF16 or E4M3) at the clocks of its own run.
+ * Used by bench.py for the e4m3 roofline denominator, for which no library GEMM figure exists.  No counterpart in
+ * the reference.
+ */
+int cfk_umma_peak(int dtype, int groups, double* flops_out, cfk_stream_t stream);
+
+/*
  * Single-CTA UMMA self-test used by the GPU test-suite to prove each operand-descriptor form
  * (K-major / MN-major shared-memory operands, A from tensor memory, 16-bit and e4m3 kinds) against
  * a CPU product.  D[128][n] (fp32, row-major) = A[128][k] * B, where B is [n][k] (b_mn_major = 0)
