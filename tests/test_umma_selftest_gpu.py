@@ -30,3 +30,22 @@ def test_umma_tile(lib, cuda, n, a_fmt, b_fmt, mn, ts):
     lib.check_device()
     # products of low-precision values summed in fp32: only the summation order differs
     assert (d.cpu() - ref).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize("dtype,per_mma", [(1, 2 * 128 * 256 * 16), (2, 2 * 128 * 256 * 32)])
+def test_umma_peak_probe_reports_its_work_and_finishes(lib, cuda, dtype, per_mma):
+    """The tensor-core ceiling probe: the returned flop count is SMs x groups x 4 UMMAs, the launch completes
+    with a clean status word, and the rate is that of a tensor core (hundreds of TFLOP/s), not of a stall."""
+    import torch
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    lib.umma_peak(dtype, 500)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    flops = lib.umma_peak(dtype, 20000)
+    e1.record()
+    torch.cuda.synchronize()
+    lib.check_device()
+    assert flops == float(sms) * 20000 * 4 * per_mma
+    tflops = flops / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    assert tflops > (600 if dtype == 1 else 1200), tflops
