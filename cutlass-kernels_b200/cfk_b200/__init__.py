@@ -37,7 +37,7 @@ class FmhaArgs(C.Structure):
         ("o_stride", C.c_int64 * 3),
         ("softmax_scale", C.c_float), ("causal", C.c_int),
         ("q_descale", C.c_float), ("k_descale", C.c_float), ("v_descale", C.c_float),
-        ("iterations", C.c_int),
+        ("iterations", C.c_int), ("v_fp16", C.c_int),
         ("s_dump", C.c_void_p),
     ]
 
@@ -100,7 +100,7 @@ class CfkLib:
                   causal=False, out_dtype=FP16, p_split_keys=-1, lse=None, mi=None, sprime=None,
                   q_descale=1.0, k_descale=1.0, v_descale=1.0, iterations=1,
                   q_stride=(0, 0, 0), k_stride=(0, 0, 0), v_stride=(0, 0, 0), o_stride=(0, 0, 0),
-                  s_dump=None) -> FmhaArgs:
+                  s_dump=None, v_fp16=False) -> FmhaArgs:
         a = FmhaArgs()
         a.dtype, a.out_dtype, a.p_split_keys = dtype, out_dtype, p_split_keys
         a.batch, a.heads, a.seqlen_q, a.seqlen_kv, a.head_dim = batch, heads, seqlen_q, seqlen_kv, head_dim
@@ -114,6 +114,7 @@ class CfkLib:
         a.q_descale, a.k_descale, a.v_descale = q_descale, k_descale, v_descale
         a.iterations = iterations
         a.s_dump = _ptr(s_dump)
+        a.v_fp16 = int(bool(v_fp16))
         return a
 
     def fmha_forward(self, *pos, stream=None, **kw) -> None:

@@ -250,7 +250,9 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != 256) return CFK_ERR_UNSUPPORTED;
   if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
   if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;
-  const int pdt = a->dtype;   // P is rounded to the input type
+  if (a->v_fp16 && (a->dtype != CFK_E4M3 || a->head_dim == 256)) return CFK_ERR_UNSUPPORTED;
+  const int vdt = a->v_fp16 ? CFK_FP16 : a->dtype;   // element type of V, and the type P is rounded to
+  const int pdt = vdt;
   const float qd = a->dtype == CFK_E4M3 ? a->q_descale : (a->q_descale == 0.f ? 1.f : a->q_descale);
   const float kd = a->dtype == CFK_E4M3 ? a->k_descale : (a->k_descale == 0.f ? 1.f : a->k_descale);
   const float vd = a->dtype == CFK_E4M3 ? a->v_descale : (a->v_descale == 0.f ? 1.f : a->v_descale);
@@ -262,7 +264,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   int64_t qs[3], ks[3], vs[3], os[3];
   if (!resolve_strides(a->q_stride, qs, a->seqlen_q, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
   if (!resolve_strides(a->k_stride, ks, a->seqlen_kv, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
-  if (!resolve_strides(a->v_stride, vs, a->seqlen_kv, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
+  if (!resolve_strides(a->v_stride, vs, a->seqlen_kv, a->heads, a->head_dim, dtype_size(vdt))) return CFK_ERR_INVALID_ARG;
   if (!resolve_strides(a->o_stride, os, a->seqlen_q, a->heads, a->head_dim, 2)) return CFK_ERR_INVALID_ARG;
 
   int err = CFK_OK;
@@ -278,7 +280,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   const int kv_spans = a->head_dim == 256 ? esz : 0;   // 128 columns = esz spans of 128 bytes
   if ((rc = encode_bshd(&L.tm_k, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 128, kv_spans)))
     return rc;
-  if ((rc = encode_bshd(&L.tm_v, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, kv_spans)))
+  if ((rc = encode_bshd(&L.tm_v, vdt, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128, kv_spans)))
     return rc;
   if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
     return rc;

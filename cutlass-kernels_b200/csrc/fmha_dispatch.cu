@@ -18,6 +18,8 @@ int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L) {
     return head_dim == 64 ? fmha_launch_f16_f16_64(L) : fmha_launch_f16_f16_128(L);
   if (dtype == CFK_BF16 && p_dtype == CFK_BF16)
     return head_dim == 64 ? fmha_launch_bf16_bf16_64(L) : fmha_launch_bf16_bf16_128(L);
+  if (dtype == CFK_E4M3 && p_dtype == CFK_FP16)
+    return head_dim == 64 ? fmha_launch_e4m3_f16_64(L) : head_dim == 128 ? fmha_launch_e4m3_f16_128(L) : CFK_ERR_UNSUPPORTED;
   if (dtype == CFK_E4M3 && p_dtype == CFK_E4M3)
     return head_dim == 64 ? fmha_launch_e4m3_e4m3_64(L) : head_dim == 128 ? fmha_launch_e4m3_e4m3_128(L) : CFK_ERR_UNSUPPORTED;
   return CFK_ERR_UNSUPPORTED;

@@ -43,7 +43,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t sQ = smem_base;                                    // 2 tiles
   const uint32_t sOst = smem_base + 2 * C::TILEB;                   // separate O staging (if any)
   const uint32_t sRing = sOst + (C::O_SEPARATE ? 2 * C::OTILEB : 0);
-  const uint32_t sBar = sRing + C::NSLOT * C::TILEB;
+  const uint32_t sBar = sRing + C::NSLOT * C::SLOTB;
   uint8_t* gBar = smem_gen + (sBar - smem_base);
   // barrier map (8 bytes each)
   const uint32_t bar_q_full = sBar;
@@ -156,8 +156,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const int slot = idx % C::NSLOT;
           const uint32_t ph = (idx / C::NSLOT) & 1;
           if (!mbar_wait(bar_kv_empty + 8 * slot, ph ^ 1u, actx, kErrFmhaKvEmpty)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_kv_full + 8 * slot, C::TILEB);
-          tma_load_5d(sRing + slot * C::TILEB, which == 0 ? &tm_k : &tm_v, bar_kv_full + 8 * slot, 0, j * C::BN, 0,
+          mbar_arrive_expect_tx(bar_kv_full + 8 * slot, which == 0 ? C::TILEB : C::VTILEB);
+          tma_load_5d(sRing + slot * C::SLOTB, which == 0 ? &tm_k : &tm_v, bar_kv_full + 8 * slot, 0, j * C::BN, 0,
                       head, batch);
         }
       }
@@ -173,10 +173,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // sub-tile; SBO = distance between groups of 8 keys).  A slot or a k-step adds a constant to the low word.
       const uint64_t aq0 = make_smem_desc(sQ, 16, C::SBO, C::SWZ);
       const uint64_t bk0 = make_smem_desc(sRing, 16, C::SBO, C::SWZ);
-      const uint64_t bv0 = make_smem_desc(sRing, C::SUBB, C::SBO, C::SWZ);
+      const uint64_t bv0 = make_smem_desc(sRing, C::VSUBB, C::VSBO, C::VSWZ);
       auto issue_qk = [&](int t, int slot) {
         const uint64_t a0 = desc_advance_lo(aq0, t * C::TILEB);
-        const uint64_t b0 = desc_advance_lo(bk0, slot * C::TILEB);
+        const uint64_t b0 = desc_advance_lo(bk0, slot * C::SLOTB);
         const uint32_t d = tmem_base + t * 128;
 #pragma unroll
         for (int kk = 0; kk < C::QK_KSTEPS; ++kk) {
@@ -187,24 +187,24 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       };
       // half 0: keys 0-63 of the tile, half 1: keys 64-127
       auto issue_pv_half = [&](int t, int slot, int half, uint32_t accumulate) {
-        const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
+        const uint64_t b0 = desc_advance_lo(bv0, slot * C::SLOTB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
         const uint32_t a = tmem_base + t * 128;
 #pragma unroll
         for (int k2 = 0; k2 < C::PV_KSTEPS / 2; ++k2) {
           const int kk = half * (C::PV_KSTEPS / 2) + k2;
-          umma_ts_e<C::KIND8, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
+          umma_ts_e<C::KIND8_PV, false>(d, a + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV,
                                      k2 > 0 ? 1u : accumulate, leader);
         }
       };
       auto issue_pv_lo = [&](int t, int slot) {
-        const uint64_t b0 = desc_advance_lo(bv0, slot * C::TILEB);
+        const uint64_t b0 = desc_advance_lo(bv0, slot * C::SLOTB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
         const uint32_t a = tmem_base + t * 128;
         {   // second term of P lives in the upper half of the S_t columns
 #pragma unroll
           for (int kk = 0; kk < C::PV_KSTEPS; ++kk)
-            umma_ts_e<C::KIND8, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
+            umma_ts_e<C::KIND8_PV, false>(d, a + 64 + kk * 8, desc_advance_lo(b0, kk * C::V_STEPB), C::IDESC_PV, 1u, leader);
         }
       };
 

@@ -25,6 +25,8 @@ int fmha_launch_f16_f16_64(const FmhaLaunch&);
 int fmha_launch_f16_f16_128(const FmhaLaunch&);
 int fmha_launch_bf16_bf16_64(const FmhaLaunch&);
 int fmha_launch_bf16_bf16_128(const FmhaLaunch&);
+int fmha_launch_e4m3_f16_64(const FmhaLaunch&);    // Q, K e4m3; V, P fp16
+int fmha_launch_e4m3_f16_128(const FmhaLaunch&);
 int fmha_launch_e4m3_e4m3_64(const FmhaLaunch&);
 int fmha_launch_e4m3_e4m3_128(const FmhaLaunch&);
 int fmha_launch_hd256_f16(const FmhaLaunch&);    // head dimension 256: tm_k / tm_v boxes are 128 keys x 128 columns,

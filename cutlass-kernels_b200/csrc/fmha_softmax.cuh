@@ -12,10 +12,14 @@ namespace cfk {
 
 template <int DT, int PT, int HD>
 struct FmhaCfg {
+  // DT: element type of Q and K; PT: element type of P and of V (they meet in the second GEMM and must be of one MMA
+  // kind).  PT == DT everywhere except the hybrid mode DT = e4m3, PT = fp16, which is what the reference runs for
+  // --prec-type=2 unless it is built with GEMM2FP8 (src/fmha-pipeline/fmha_forward.cu:446-450).
   static constexpr int ESZ = (DT == kDtE4M3) ? 1 : 2;
   static constexpr int PESZ = (PT == kDtE4M3) ? 1 : 2;
-  static_assert(ESZ == PESZ, "P and V must share an MMA kind");
-  static constexpr bool KIND8 = (ESZ == 1);
+  static_assert(ESZ == PESZ || (DT == kDtE4M3 && PT == kDtF16), "unsupported mix of operand types");
+  static constexpr bool KIND8 = (ESZ == 1);        // MMA kind of Q K^T
+  static constexpr bool KIND8_PV = (PESZ == 1);    // MMA kind of P V
   static constexpr int BM = 128, BN = 128;
   static constexpr int ROWB = HD * ESZ;            // bytes per row of a Q/K/V tile
   static constexpr int SPANB = ROWB < 128 ? ROWB : 128;   // swizzle span: 128 bytes, or the whole 64-byte row (e4m3, d = 64)
@@ -25,7 +29,15 @@ struct FmhaCfg {
   static constexpr int KSPS = SPANB / 32;          // UMMA k-steps (32 bytes of reduction) per span
   static constexpr int NSUB = ROWB / SPANB;        // span-wide sub-tiles per tile
   static constexpr int SUBB = 128 * SPANB;         // bytes per sub-tile (128 rows x one span)
-  static constexpr int TILEB = NSUB * SUBB;        // bytes per Q/K/V tile
+  static constexpr int TILEB = NSUB * SUBB;        // bytes per Q/K tile
+  // V tile: same quantities for rows of HD * PESZ bytes
+  static constexpr int VROWB = HD * PESZ;
+  static constexpr int VSPANB = VROWB < 128 ? VROWB : 128;
+  static constexpr uint32_t VSWZ = VSPANB == 128 ? kSwizzle128B : kSwizzle64B;
+  static constexpr int VSBO = 8 * VSPANB;
+  static constexpr int VSUBB = 128 * VSPANB;
+  static constexpr int VTILEB = (VROWB / VSPANB) * VSUBB;
+  static constexpr int SLOTB = VTILEB > TILEB ? VTILEB : TILEB;   // ring slot: holds a K tile or a V tile
   static constexpr int ONSUB = HD * 2 / 128;       // output is always 16 bit, in 128-byte spans
   static constexpr int OSUBB = 128 * 128;
   static constexpr int OTILEB = ONSUB * OSUBB;
@@ -33,20 +45,20 @@ struct FmhaCfg {
   static constexpr int SMEM_LIMIT = 232448;
   static constexpr int FIXEDB = 2 * TILEB + (O_SEPARATE ? 2 * OTILEB : 0);
   static constexpr int BARB = 512;
-  static constexpr int NSLOT_FIT = (SMEM_LIMIT - 1024 - BARB - FIXEDB) / TILEB;
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - 1024 - BARB - FIXEDB) / SLOTB;
   static constexpr int NSLOT = NSLOT_FIT > 8 ? 8 : NSLOT_FIT;
   static_assert(NSLOT >= 3, "ring too small");
-  static constexpr int SMEM_BYTES = 1024 + FIXEDB + NSLOT * TILEB + BARB;
+  static constexpr int SMEM_BYTES = 1024 + FIXEDB + NSLOT * SLOTB + BARB;
   static constexpr int QK_KSTEPS = ROWB / 32;      // each UMMA consumes 32 bytes of K extent
-  static constexpr int PV_KSTEPS = BN * ESZ / 32;
-  static constexpr int V_STEPB = (32 / ESZ) * SPANB;   // bytes between successive 32-byte-K groups of V rows
+  static constexpr int PV_KSTEPS = BN * PESZ / 32;
+  static constexpr int V_STEPB = (32 / PESZ) * VSPANB;   // bytes between the key groups of successive UMMAs of P V
   static constexpr int PCOLS = BN * PESZ / 4;      // TMEM columns taken by P
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL0 = 256;
   static constexpr uint32_t FMT_IN = (DT == kDtBF16) ? kFmtBF16 : 0u;   // f16 / e4m3 are both code 0
   static constexpr uint32_t FMT_P = (PT == kDtBF16) ? kFmtBF16 : 0u;
   static constexpr uint32_t IDESC_QK = make_idesc(1, FMT_IN, FMT_IN, 0, 0, BM, BN);
-  static constexpr uint32_t IDESC_PV = make_idesc(1, FMT_P, FMT_IN, 0, 1, BM, HD);
+  static constexpr uint32_t IDESC_PV = make_idesc(1, FMT_P, FMT_P, 0, 1, BM, HD);   // A = P and B = V share PT
   static constexpr int NTHREADS = 384;
   // Register budget after setmaxnreg.  The pool is what the CTA was launched with: 384 threads at the
   // 168 registers a 384-thread launch bound allows.  setmaxnreg.inc blocks until the registers it asks

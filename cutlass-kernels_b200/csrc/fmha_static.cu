@@ -87,6 +87,7 @@ extern "C" int cfk_fmha_forward_static(const cfk_fmha_args* a, cfk_stream_t stre
   if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_E4M3) return CFK_ERR_INVALID_ARG;
   if (a->out_dtype != CFK_FP16 && a->out_dtype != CFK_BF16) return CFK_ERR_INVALID_ARG;
   if (a->head_dim != 64 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
+  if (a->v_fp16) return CFK_ERR_UNSUPPORTED;   // the hybrid e4m3 / fp16 mode goes through cfk_fmha_forward
   if (a->dtype == CFK_E4M3 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
   if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
   if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;

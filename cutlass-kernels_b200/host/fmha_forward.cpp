@@ -27,7 +27,7 @@ struct e4m3_t { unsigned char bits; };   // 1-byte element: cfk::dtype_of falls 
 
 struct Options {
   int batch = 4, dim = 2048, head = 64, seq = 4096, iterations = 20, prec = 2, streams = 1, check_heads = 2;
-  bool check = false, causal = false, help = false, verify_all = false;
+  bool check = false, causal = false, help = false, verify_all = false, hybrid = false;
   unsigned long long seed = 3080;
 };
 
@@ -56,6 +56,7 @@ static Options parse(int argc, char** argv) {
     else if (flag(argv[i], "reference-check", &v)) o.check = (v == "true" || v == "1");
     else if (flag(argv[i], "causal", &v)) o.causal = (v == "true" || v == "1");
     else if (flag(argv[i], "verify-all", &v)) o.verify_all = o.check = (v == "true" || v == "1");
+    else if (flag(argv[i], "hybrid-fp8", &v)) o.hybrid = (v == "true" || v == "1");
     else std::fprintf(stderr, "ignoring unknown argument %s\n", argv[i]);
   }
   return o;
@@ -114,29 +115,33 @@ static void host_attention_head(const std::vector<float>& q, const std::vector<f
   }
 }
 
-template <typename T, int HEADDIM>
+// T: element type of Q and K; TV: of V (T, or __half in the hybrid e4m3 mode)
+template <typename T, int HEADDIM, typename TV = T>
 static int run(const Options& o, int dtype) {
+  const int dtype_v = sizeof(TV) == sizeof(T) ? dtype : CFK_FP16;
   const int B = o.batch, S = o.seq, D = HEADDIM, H = o.dim / D;
   std::printf("M = %d\nN = %d\nK = %d\nQBLK = 128\nKBLK = 128\nL = %d : %d\n", S, S, D, B, H);
   const size_t n = (size_t)B * S * H * D;
-  T *q, *k, *v;
+  T *q, *k;
+  TV* v;
   __half* out;
   float *mi, *sprime;
   CUDA_OK(cudaMalloc(&q, n * sizeof(T)));
   CUDA_OK(cudaMalloc(&k, n * sizeof(T)));
-  CUDA_OK(cudaMalloc(&v, n * sizeof(T)));
+  CUDA_OK(cudaMalloc(&v, n * sizeof(TV)));
   CUDA_OK(cudaMalloc(&out, n * sizeof(__half)));
   CUDA_OK(cudaMalloc(&mi, (size_t)B * H * S * sizeof(float)));
   CUDA_OK(cudaMalloc(&sprime, (size_t)B * H * S * sizeof(float)));
   // Gaussian inputs, seeds base+1/+2/+3 as the reference (fmha_forward.cu:479,498-500); e4m3 inputs are
   // quantised with a per-tensor scale amax/448 (the reference casts N(0,1) straight to e4m3).
   float descale[3] = {1.f, 1.f, 1.f};
-  T* ptr[3] = {q, k, v};
+  void* ptr[3] = {q, k, v};
+  const int pdt[3] = {dtype, dtype, dtype_v};
   for (int i = 0; i < 3; ++i) {
-    if (dtype == CFK_E4M3) {
+    if (pdt[i] == CFK_E4M3) {
       descale[i] = 6.0f / 448.0f;   // N(0,1) draws of this generator stay within +-6
-      if (cfk_fill(ptr[i], dtype, (int64_t)n, o.seed + 1 + i, 0, 0, 1.0f / descale[i], 0.f, nullptr)) return 1;
-    } else if (cfk_fill(ptr[i], dtype, (int64_t)n, o.seed + 1 + i, 0, 0, 1.f, 0.f, nullptr)) {
+      if (cfk_fill(ptr[i], pdt[i], (int64_t)n, o.seed + 1 + i, 0, 0, 1.0f / descale[i], 0.f, nullptr)) return 1;
+    } else if (cfk_fill(ptr[i], pdt[i], (int64_t)n, o.seed + 1 + i, 0, 0, 1.f, 0.f, nullptr)) {
       return 1;
     }
   }
@@ -148,14 +153,14 @@ static int run(const Options& o, int dtype) {
   const float scale = 1.4426950408889634f / std::sqrt((float)D);   // log2(e)/sqrt(D), fmha_forward.cu:452-454
 
   // warm-up (10 launches), then `iterations` back-to-back launches between two events
-  fmhaForwardDeviceLoop<T, T, float, __half, HEADDIM>(S, S, H, B, q, k, v, (T*)nullptr, out, mi, sprime, 10, o.streams,
+  fmhaForwardDeviceLoop<T, TV, float, __half, HEADDIM>(S, S, H, B, q, k, v, (T*)nullptr, out, mi, sprime, 10, o.streams,
                                                      scale, 0);
   CUDA_OK(cudaDeviceSynchronize());
   cudaEvent_t e0, e1;
   CUDA_OK(cudaEventCreate(&e0));
   CUDA_OK(cudaEventCreate(&e1));
   CUDA_OK(cudaEventRecord(e0, 0));
-  fmhaForwardDeviceLoop<T, T, float, __half, HEADDIM>(S, S, H, B, q, k, v, (T*)nullptr, out, mi, sprime, o.iterations,
+  fmhaForwardDeviceLoop<T, TV, float, __half, HEADDIM>(S, S, H, B, q, k, v, (T*)nullptr, out, mi, sprime, o.iterations,
                                                      o.streams, scale, 0);
   CUDA_OK(cudaEventRecord(e1, 0));
   CUDA_OK(cudaDeviceSynchronize());
@@ -181,7 +186,7 @@ static int run(const Options& o, int dtype) {
     CUDA_OK(cudaMalloc(&tmp, nb * sizeof(float)));
     for (int i = 0; i < 3; ++i) {
       hf[i].resize(nb);
-      if (cfk_convert(ptr[i], dtype, tmp, CFK_FP32, (int64_t)nb, descale[i], nullptr)) return 1;
+      if (cfk_convert(ptr[i], pdt[i], tmp, CFK_FP32, (int64_t)nb, descale[i], nullptr)) return 1;
       CUDA_OK(cudaMemcpy(hf[i].data(), tmp, nb * sizeof(float), cudaMemcpyDeviceToHost));
     }
     std::vector<float> ho(nb);
@@ -197,7 +202,7 @@ static int run(const Options& o, int dtype) {
         CUDA_OK(cudaMalloc(&sdump, (size_t)B * H * S * S * sizeof(T)));
         CUDA_OK(cudaMemset(sdump, 0, (size_t)B * H * S * S * sizeof(T)));
         lo.dump_scores = true;
-        fmhaForwardDevice<T, T, float, __half, HEADDIM>(S, S, H, B, q, k, v, sdump, out, mi, sprime, 1, scale, 0);
+        fmhaForwardDevice<T, TV, float, __half, HEADDIM>(S, S, H, B, q, k, v, sdump, out, mi, sprime, 1, scale, 0);
         lo.dump_scores = false;
         CUDA_OK(cudaDeviceSynchronize());
         if (cfk::last_status() != CFK_OK) return 1;
@@ -269,7 +274,8 @@ int main(int argc, char** argv) {
   if (o.help) {
     std::printf("fmha_forward --batch-size=<int> --dim-size=<int> --head-size=<64|128|256> --seq-length=<int>\n"
                 "             --iterations=<int> --prec-type=<1 fp16|2 e4m3|3 bf16> --num-cuda-streams=<int>\n"
-                "             --reference-check=<bool> --verify-all=<bool> --causal=<bool> --check-heads=<int> --seed=<int>\n");
+                "             --reference-check=<bool> --verify-all=<bool> --causal=<bool> --check-heads=<int> --seed=<int>\n"
+                "             --hybrid-fp8=<bool> (prec-type 2 only: V in fp16)\n");
     return 0;
   }
   if (o.head != 64 && o.head != 128 && o.head != 256) {
@@ -284,6 +290,10 @@ int main(int argc, char** argv) {
            : o.head == 128 ? run<__nv_bfloat16, 128>(o, CFK_BF16)
                            : run<__nv_bfloat16, 256>(o, CFK_BF16);
   if (o.prec == 2) {
+    if (o.hybrid) {   // Q, K e4m3 and V fp16: the reference's FP8 mode when it is built without GEMM2FP8
+      if (o.head == 256) { std::printf("hybrid-fp8 runs at head sizes 64 and 128\n"); return 1; }
+      return o.head == 64 ? run<e4m3_t, 64, __half>(o, CFK_E4M3) : run<e4m3_t, 128, __half>(o, CFK_E4M3);
+    }
     return o.head == 64 ? run<e4m3_t, 64>(o, CFK_E4M3)
            : o.head == 128 ? run<e4m3_t, 128>(o, CFK_E4M3) : run<e4m3_t, 256>(o, CFK_E4M3);
   }

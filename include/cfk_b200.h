@@ -75,6 +75,10 @@ typedef struct cfk_fmha_args {
   int causal;     /* key j visible to query i iff j <= i + (seqlen_kv - seqlen_q) */
   float q_descale, k_descale, v_descale; /* multiply the stored values to get real ones; use 1 for 16-bit */
   int iterations; /* number of back-to-back launches (the reference's loop, fmha_forward.cu:375-382) */
+  int v_fp16;     /* e4m3 inputs only: 1 = V is fp16 (strides in fp16 elements) and P is rounded to fp16, while Q and K
+                     are e4m3: what the reference runs for --prec-type=2 unless it is built with GEMM2FP8
+                     (src/fmha-pipeline/fmha_forward.cu:446-450).  Head dimensions 64 and 128.  0 = V has the type
+                     of Q and K. */
   void* s_dump;   /* optional, debugging only: [batch][heads][seqlen_q][seqlen_kv], the reference's S of a COPYOUTMM0
                      build (fmha_consumer.h:31-42): Q K^T before the softmax scale and before masking, rounded to the
                      input type (fp16 for e4m3 inputs, in stored units).  Key tiles a causal mask skips are not

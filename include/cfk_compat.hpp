@@ -78,7 +78,9 @@ void fmhaForwardDevice(int SEQLEN, int KEYLEN, int NUMHEADS, int BATCH, PrecType
                        int iterations, float scale, cudaStream_t stream = 0) {
   static_assert(std::is_same<SoftType, float>::value, "softmax statistics are fp32");
   static_assert(sizeof(OutputType) == 2, "the output is a 16-bit type");
-  static_assert(sizeof(PrecType) == sizeof(Gemm2Type), "Q/K and V share one element type here");
+  // Gemm2Type differs from PrecType only in the reference's FP8 mode without GEMM2FP8: Q, K e4m3 and V half
+  static_assert(sizeof(PrecType) == sizeof(Gemm2Type) || (sizeof(PrecType) == 1 && sizeof(Gemm2Type) == 2),
+                "V has the type of Q and K, or is a 16-bit float while Q and K are e4m3");
   const cfk::LaunchOptions& opt = cfk::launch_options();
   cfk_fmha_args a{};
   a.dtype = cfk::dtype_of<PrecType>::value;
@@ -92,6 +94,7 @@ void fmhaForwardDevice(int SEQLEN, int KEYLEN, int NUMHEADS, int BATCH, PrecType
   a.q_descale = opt.q_descale; a.k_descale = opt.k_descale; a.v_descale = opt.v_descale;
   a.iterations = iterations;
   a.s_dump = (opt.dump_scores && sizeof(PrecType) == 2) ? S : nullptr;   // else S is ignored (may be nullptr)
+  a.v_fp16 = sizeof(PrecType) == 1 && sizeof(Gemm2Type) == 2;
   cfk::note_status("fmhaForwardDevice", cfk_fmha_forward(&a, stream));
 }
 

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_struct_layout_matches_header(lib):
     # sizes as the C compiler lays them out for the declarations in the header
-    assert C.sizeof(cfk_b200.FmhaArgs) == 8 * 4 + 7 * 8 + 12 * 8 + 4 + 4 + 3 * 4 + 4 + 8
+    assert C.sizeof(cfk_b200.FmhaArgs) == 8 * 4 + 7 * 8 + 12 * 8 + 4 + 4 + 3 * 4 + 4 + (4 + 4) + 8   # v_fp16 + padding
     assert C.sizeof(cfk_b200.GemmArgs) == 5 * 4 + 4 + 3 * 8 + 4 * 4 + 8
 
 

@@ -269,3 +269,24 @@ def test_fmha_score_dump_is_raw_q_k_transposed(lib, cuda, dtype, D, causal, kern
         assert not written[0, 0][0, 256:].any()      # row 0 sees keys 0..124; tiles from key 256 on are never computed
     tol = np.abs(ref) * 2.0 ** (-10 if dtype == 0 else -7) + 1e-3
     assert (np.abs(got - ref)[written] <= tol[written]).all()
+
+
+@pytest.mark.parametrize("B,Sq,Skv,H,D,causal", [(1, 1024, 1024, 2, 128, False), (1, 640, 640, 2, 128, True),
+                                                 (2, 512, 512, 2, 64, False), (1, 333, 500, 1, 64, True)])
+def test_fmha_hybrid_e4m3_qk_fp16_v(lib, oracle, cuda, B, Sq, Skv, H, D, causal):
+    """Q and K in e4m3, V in fp16 and P rounded to fp16: what the reference runs for --prec-type=2 when it is not built
+    with GEMM2FP8 (src/fmha-pipeline/fmha_forward.cu:446-450).  The oracle sees the de-quantised Q, K and the fp16 V;
+    with P and V at fp16 precision the result meets the 16-bit bound, not only the e4m3 one."""
+    low8, f32_8, scales = make_qkv(2, B, Sq, Skv, H, D, seed=21 + Sq)
+    low16, f32_16, _ = make_qkv(0, B, Sq, Skv, H, D, seed=21 + Sq)       # same draws, rounded to fp16
+    q, k, v = low8[0].cuda(), low8[1].cuda(), low16[2].cuda()
+    o = torch.full((B, Sq, H, D), -1.0, device="cuda", dtype=torch.float16)
+    lse = torch.zeros(B, H, Sq, device="cuda", dtype=torch.float32)
+    lib.fmha_forward(q, k, v, o, dtype=2, batch=B, heads=H, seqlen_q=Sq, seqlen_kv=Skv, head_dim=D,
+                     softmax_scale=1.0 / math.sqrt(D), causal=causal, q_descale=scales[0], k_descale=scales[1],
+                     v_descale=1.0, lse=lse, v_fp16=True)
+    lib.check_device()
+    ref = oracle.attention(f32_8[0], f32_8[1], f32_16[2], 1.0 / math.sqrt(D), causal)
+    cmp = oracle.compare(o.float().cpu().numpy(), ref["o"])
+    assert cmp["nonfinite"] == 0 and cmp["max_abs"] <= 2e-3, cmp
+    assert np.abs(lse.cpu().numpy() - ref["lse"]).max() <= 2e-3
