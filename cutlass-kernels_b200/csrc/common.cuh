@@ -418,6 +418,16 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, u
         : "memory");
   }
 }
+// fp32 operands run as tf32: 8 elements (32 bytes) of reduction per instruction (the reference runs its fp32 GEMM
+// type the same way, src/cute-gemm-tma-gma/gemm.cu:355-356).
+__device__ __forceinline__ void umma_ss_pair_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // The same with A in tensor memory (each CTA's own 128 rows, same column address in both).
 template <bool KIND8>
 __device__ __forceinline__ void umma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,

@@ -38,6 +38,7 @@ struct GemmParams {
   const void* src;       // matrix of the beta term (same layout as D); D itself when the update is in place
   float alpha, beta;
   int bf16;
+  int tf32;              // operands and D are fp32; the tensor core runs them as tf32 (kind::tf32, 8 elements per k-step)
   int tiles_r, tiles_c;  // 256 x 256 tiles
   int* status;
 };
@@ -88,7 +89,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
   const uint32_t rank = cluster_ctarank();
   const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int total_tiles = p.tiles_r * p.tiles_c * p.L;
-  const int nkb = (p.K + C::BK - 1) / C::BK;
+  const int bk = p.tf32 ? C::BK / 2 : C::BK;   // elements per 128-byte stage row
+  const int nkb = (p.K + bk - 1) / bk;
 
   // Both CTAs of a pair read the same word, so they skip or run together.
   if (cta_should_skip(p.status)) return;
@@ -122,8 +124,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, actx, kErrGemmEmpty)) { ok = false; break; }
           const uint32_t leader_full = map_to_cta(bar_full + 8 * s, 0);
           mbar_arrive_expect_tx_cluster(leader_full, C::XB + C::YB);
-          tma_load_3d_pair(sX + s * C::XB, &tm_x, leader_full, kb * C::BK, tr * C::TILE + (int)rank * C::BM, b);
-          tma_load_3d_pair(sY + s * C::YB, &tm_y, leader_full, kb * C::BK, tc * C::TILE + (int)rank * C::BNH, b);
+          tma_load_3d_pair(sX + s * C::XB, &tm_x, leader_full, kb * bk, tr * C::TILE + (int)rank * C::BM, b);
+          tma_load_3d_pair(sY + s * C::YB, &tm_y, leader_full, kb * bk, tc * C::TILE + (int)rank * C::BNH, b);
         }
       }
     }
@@ -131,7 +133,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc_f16 = make_idesc(1, kFmtF16, kFmtF16, 0, 0, C::TILE, C::TILE);
       constexpr uint32_t idesc_bf16 = make_idesc(1, kFmtBF16, kFmtBF16, 0, 0, C::TILE, C::TILE);
-      const uint32_t idesc = p.bf16 ? idesc_bf16 : idesc_f16;
+      constexpr uint32_t idesc_tf32 = make_idesc(1, 2u, 2u, 0, 0, C::TILE, C::TILE);   // kind::tf32: format code 2
+      const uint32_t idesc = p.tf32 ? idesc_tf32 : (p.bf16 ? idesc_bf16 : idesc_f16);
       int idx = 0, local = 0;
       bool ok = true;
       for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
@@ -146,10 +149,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
           tc_fence_after_sync();
           const uint64_t a0 = make_smem_desc(sX + s * C::XB, 16, 1024, kSwizzle128B);
           const uint64_t b0 = make_smem_desc(sY + s * C::YB, 16, 1024, kSwizzle128B);
+          if (p.tf32) {
 #pragma unroll
-          for (int kk = 0; kk < C::BK / 16; ++kk)
-            umma_ss_pair<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc,
-                                (kb | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < 4; ++kk)   // 32 bytes of reduction per UMMA: 8 tf32 elements
+              umma_ss_pair_tf32(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < C::BK / 16; ++kk)
+              umma_ss_pair<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc,
+                                  (kb | kk) != 0 ? 1u : 0u);
+          }
           umma_commit_pair(bar_empty + 8 * s);                  // this CTA's stage
           umma_commit_pair(map_to_cta(bar_empty + 8 * s, 1));   // the peer's stage
         }
@@ -183,7 +192,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
         uint32_t acc[32];
         tmem_ld_x32(tmem_base + lane_base + buf * 256 + c * 32, acc);
         tmem_wait_ld();
-        if (row < p.R) {
+        if (row < p.R && p.tf32) {
+          float* drow32 = reinterpret_cast<float*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+          const float* srow32 = reinterpret_cast<const float*>(p.src) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {   // 4 columns = 16 bytes per group
+            const int col = col0 + c * 32 + g * 4;
+            if (col < p.Cn) {
+              float4 v;
+              v.x = p.alpha * __uint_as_float(acc[g * 4]);     v.y = p.alpha * __uint_as_float(acc[g * 4 + 1]);
+              v.z = p.alpha * __uint_as_float(acc[g * 4 + 2]); v.w = p.alpha * __uint_as_float(acc[g * 4 + 3]);
+              if (p.beta != 0.f) {
+                const float4 old = *reinterpret_cast<const float4*>(srow32 + c * 32 + g * 4);
+                v.x += p.beta * old.x; v.y += p.beta * old.y; v.z += p.beta * old.z; v.w += p.beta * old.w;
+              }
+              *reinterpret_cast<float4*>(drow32 + c * 32 + g * 4) = v;
+            }
+          }
+        } else if (row < p.R) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
             const int col = col0 + c * 32 + g * 8;
@@ -244,7 +270,7 @@ using namespace cfk;
 extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   if (!a || !a->a || !a->b || !a->c) return CFK_ERR_INVALID_ARG;
   if (a->m <= 0 || a->n <= 0 || a->k <= 0 || a->l <= 0 || a->iterations < 0) return CFK_ERR_INVALID_ARG;
-  if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16) return CFK_ERR_UNSUPPORTED;
+  if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_FP32) return CFK_ERR_UNSUPPORTED;
   if ((a->m % 8) || (a->n % 8) || (a->k % 8)) return CFK_ERR_UNSUPPORTED;
   if (((uintptr_t)a->a | (uintptr_t)a->b | (uintptr_t)a->c | (uintptr_t)a->c_src) & 15u) return CFK_ERR_INVALID_ARG;
 
@@ -260,12 +286,14 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   const int Cn = a->c_row_major ? a->n : a->m;
 
   CUtensorMap tm_x, tm_y;
+  const uint64_t esz = (uint64_t)dtype_size(a->dtype);
+  const uint32_t bk = (uint32_t)(128 / esz);                   // one 128-byte span of the reduction per stage
   const uint64_t xd[3] = {(uint64_t)a->k, (uint64_t)R, (uint64_t)a->l};
-  const uint64_t xs[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)R};
-  const uint32_t xb[3] = {GemmCfg::BK, GemmCfg::BM, 1};       // per CTA: 128 rows of X
+  const uint64_t xs[2] = {(uint64_t)a->k * esz, (uint64_t)a->k * esz * (uint64_t)R};
+  const uint32_t xb[3] = {bk, GemmCfg::BM, 1};                 // per CTA: 128 rows of X
   const uint64_t yd[3] = {(uint64_t)a->k, (uint64_t)Cn, (uint64_t)a->l};
-  const uint64_t ys[2] = {(uint64_t)a->k * 2, (uint64_t)a->k * 2 * (uint64_t)Cn};
-  const uint32_t yb[3] = {GemmCfg::BK, GemmCfg::BNH, 1};      // per CTA: 128 rows of Y
+  const uint64_t ys[2] = {(uint64_t)a->k * esz, (uint64_t)a->k * esz * (uint64_t)Cn};
+  const uint32_t yb[3] = {bk, GemmCfg::BNH, 1};                // per CTA: 128 rows of Y
   int rc;
   if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, 128))) return rc;
   if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, 128))) return rc;
@@ -279,6 +307,7 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   p.src = a->c_src ? a->c_src : a->c;
   p.alpha = a->alpha; p.beta = a->beta;
   p.bf16 = a->dtype == CFK_BF16;
+  p.tf32 = a->dtype == CFK_FP32;
   p.tiles_r = (R + GemmCfg::TILE - 1) / GemmCfg::TILE;
   p.tiles_c = (Cn + GemmCfg::TILE - 1) / GemmCfg::TILE;
   p.status = status;

@@ -5,7 +5,8 @@
 // sample of entries against a float64 dot product of the same operands, to fp16 output rounding.
 //
 //   gemm [type=3] [m=5120] [n=5120] [k=4096] [l=1] [iterations=100] [alpha=1] [beta=0]
-//   type 3 = fp16, type 4 = bf16 (addition).  Types 1/2 of the reference (fp32 as tf32, fp64) are not built.
+//   type 1 = fp32 operands with tf32 products (as the reference runs them, gemm.cu:355-356), type 3 = fp16,
+//   type 4 = bf16 (addition).  Type 2 of the reference (fp64) is not built.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -65,7 +66,9 @@ static int run(int dtype, int m, int n, int k, int l, int iterations, float alph
   CUDA_OK(cudaMemcpy(hb.data(), tmp2, hb.size() * sizeof(float), cudaMemcpyDeviceToHost));
   cudaFree(tmp2);
   cudaFree(tmp);
-  const double ulp = dtype == CFK_FP16 ? std::ldexp(1.0, -10) : std::ldexp(1.0, -7);
+  // output rounding of the 16-bit types; for tf32 the operands lose their low 13 mantissa bits in the product
+  const double ulp = dtype == CFK_FP16 ? std::ldexp(1.0, -10) : dtype == CFK_BF16 ? std::ldexp(1.0, -7) : 0.0;
+  const double tf32_abs = dtype == CFK_FP32 ? 2.0 * std::ldexp(1.0, -11) * std::sqrt((double)k) : 0.0;
   int failures = 0;
   unsigned long long s = 12345;
   for (int t = 0; t < 4096; ++t) {
@@ -78,7 +81,7 @@ static int run(int dtype, int m, int n, int k, int l, int iterations, float alph
     double want = alpha * acc;
     if (beta != 0.f) want += (double)beta * hc0[(size_t)j * m + i];
     const double got = hc[(size_t)j * m + i];
-    if (std::fabs(got - want) > ulp * std::fmax(1.0, std::fabs(want)) + 1e-3) {
+    if (std::fabs(got - want) > ulp * std::fmax(1.0, std::fabs(want)) + 1e-3 + tf32_abs) {
       if (failures < 5) std::printf("C[%d,%d]: got %g want %g\n", i, j, got, want);
       ++failures;
     }
@@ -121,8 +124,9 @@ int main(int argc, char** argv) {
   if (argc > 6) iterations = std::atoi(argv[6]);
   if (argc > 7) alpha = (float)std::atof(argv[7]);
   if (argc > 8) beta = (float)std::atof(argv[8]);
+  if (type == 1) return run<float>(CFK_FP32, m, n, k, l, iterations, alpha, beta);
   if (type == 3) return run<__half>(CFK_FP16, m, n, k, l, iterations, alpha, beta);
   if (type == 4) return run<__nv_bfloat16>(CFK_BF16, m, n, k, l, iterations, alpha, beta);
-  std::printf("type %d is not built (3 = fp16, 4 = bf16)\n", type);
+  std::printf("type %d is not built (1 = fp32 as tf32, 3 = fp16, 4 = bf16)\n", type);
   return 1;
 }

@@ -118,7 +118,8 @@ int cfk_fmha_forward_static(const cfk_fmha_args* args, cfk_stream_t stream);
  * K must be a multiple of 8 and M, N multiples of 8; pointers 16-byte aligned.
  */
 typedef struct cfk_gemm_args {
-  int dtype;      /* FP16 or BF16 for A, B and C */
+  int dtype;      /* FP16 or BF16 for A, B and C; FP32: fp32 A, B and C with the products taken in tf32, the
+                     reference's fp32 GEMM type (src/cute-gemm-tma-gma/gemm.cu:355-356, 677-678) */
   int m, n, k, l;
   const void* a;
   const void* b;

@@ -137,7 +137,8 @@ template <typename TA, typename TB, typename TC, typename Alpha, typename Beta>
 void gemm(int m, int n, int k, Alpha alpha, TA const* A, int ldA, TB const* B, int ldB, Beta beta, TC* C, int ldC,
           TA* A_out = nullptr, TB* B_out = nullptr, int L = 1, cudaStream_t stream = 0) {
   (void)ldA; (void)ldB; (void)ldC; (void)A_out; (void)B_out;
-  static_assert(sizeof(TA) == 2 && sizeof(TB) == 2 && sizeof(TC) == 2, "16-bit operands and output");
+  static_assert(sizeof(TA) == sizeof(TB) && sizeof(TA) == sizeof(TC) && (sizeof(TA) == 2 || sizeof(TA) == 4),
+                "16-bit operands and output, or fp32 operands and output (products in tf32)");
   cfk_gemm_args g{};
   g.dtype = cfk::dtype_of<TA>::value;
   g.m = m; g.n = n; g.k = k; g.l = L;

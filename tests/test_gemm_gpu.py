@@ -98,3 +98,30 @@ def test_cutlass_gemm_cli_reports_passed(cuda):
     assert out.returncode == 0, out.stdout + out.stderr
     assert "Disposition: Passed" in out.stdout
     assert "Problem Size: 512x384x256" in out.stdout and "GFLOPS:" in out.stdout
+
+
+@pytest.mark.parametrize("M,N,K,row_major", [(256, 512, 256, False), (1000, 776, 264, True), (2048, 1024, 2048, False)])
+def test_gemm_fp32_operands_as_tf32(lib, oracle, cuda, M, N, K, row_major):
+    """fp32 A, B, C with tf32 products (the reference's fp32 GEMM type, src/cute-gemm-tma-gma/gemm.cu:355-356):
+    exact against the oracle when the operands are already tf32 numbers, and within tf32 operand rounding otherwise."""
+    g = torch.Generator().manual_seed(3)
+    a = torch.rand(M, K, generator=g) * 2 - 1
+    b = torch.rand(N, K, generator=g) * 2 - 1
+    c0 = torch.rand(M, N, generator=g) * 2 - 1
+
+    def call(a_, b_):
+        c = (c0 if row_major else c0.T).contiguous().cuda()
+        lib.gemm(a_.cuda(), b_.cuda(), c, dtype=3, m=M, n=N, k=K, alpha=0.5, beta=2.0, c_row_major=row_major)
+        lib.check_device()
+        out = c.cpu()
+        return (out if row_major else out.T).double()
+
+    def tf32(x):   # keep 10 mantissa bits (truncate the low 13)
+        return (x.view(torch.int32) & ~0x1fff).view(torch.float32)
+
+    at, bt = tf32(a.clone()), tf32(b.clone())
+    exact = 0.5 * (at.double() @ bt.double().T) + 2.0 * c0.double()
+    # only the fp32 accumulation of K exact products remains (the tensor core does not round each add to nearest)
+    assert (call(at, bt) - exact).abs().max() <= K * 2.0 ** -23 * float(exact.abs().max())
+    full = 0.5 * (a.double() @ b.double().T) + 2.0 * c0.double()
+    assert (call(a, b) - full).abs().max() <= 2.0 ** -10 * K ** 0.5
