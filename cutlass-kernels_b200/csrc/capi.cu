@@ -239,7 +239,10 @@ static bool resolve_strides(const int64_t in[3], int64_t out[3], int S, int H, i
   return true;
 }
 
-extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
+// Argument checks, TMA descriptors, kernel parameters and kernel choice of one FMHA call: everything of the launch
+// except the status pointer and the stream, which the two entry points supply (allocated block / static array).
+// *p_dtype receives the type P is rounded to (and V is stored in).
+int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   if (!a || !a->q || !a->k || !a->v || !a->o) return CFK_ERR_INVALID_ARG;
   if (a->batch <= 0 || a->heads <= 0 || a->seqlen_q <= 0 || a->seqlen_kv <= 0 || a->iterations < 0)
     return CFK_ERR_INVALID_ARG;
@@ -267,11 +270,7 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   if (!resolve_strides(a->v_stride, vs, a->seqlen_kv, a->heads, a->head_dim, dtype_size(vdt))) return CFK_ERR_INVALID_ARG;
   if (!resolve_strides(a->o_stride, os, a->seqlen_q, a->heads, a->head_dim, 2)) return CFK_ERR_INVALID_ARG;
 
-  int err = CFK_OK;
-  int* status = device_status_block(&err);
-  if (!status) return err;
-
-  FmhaLaunch L;
+  FmhaLaunch& L = *out;
   std::memset(&L, 0, sizeof(L));
   int rc;
   if ((rc = encode_bshd(&L.tm_q, a->dtype, a->q, a->batch, a->seqlen_q, a->heads, a->head_dim, qs[0], qs[1], qs[2], 128)))
@@ -304,7 +303,6 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
   p.out_scale = vd;
   p.lse = a->lse; p.mi = a->mi; p.sprime = a->sprime;
   p.s_dump = a->s_dump; p.s_dump_bf16 = a->dtype == CFK_BF16;
-  p.status = status;
   L.iterations = a->iterations;
   L.exp_emu = g_tunable[CFK_TUNE_FMHA_EXP_EMU].load();
   if (L.exp_emu < 0) L.exp_emu = a->dtype == CFK_E4M3 ? 2 : 1;
@@ -317,6 +315,19 @@ extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
     p.group = (int)(grp < 1 ? 1 : (grp > bh ? bh : grp));
   }
   if ((long long)p.nqblk * a->heads * a->batch > 0x7fffffffLL) return CFK_ERR_UNSUPPORTED;
+  *p_dtype = pdt;
+  return CFK_OK;
+}
+
+extern "C" int cfk_fmha_forward(const cfk_fmha_args* a, cfk_stream_t stream) {
+  FmhaLaunch L;
+  int pdt = 0;
+  const int rc = fmha_prepare(a, &L, &pdt);
+  if (rc != CFK_OK) return rc;
+  int err = CFK_OK;
+  int* status = device_status_block(&err);
+  if (!status) return err;
+  L.p.status = status;
   L.stream = (cudaStream_t)stream;
   return fmha_dispatch(a->dtype, pdt, a->head_dim, L);
 }

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "../../include/cfk_b200.h"
 #include "fmha_params.h"
 
 namespace cfk {
@@ -36,5 +37,9 @@ int fmha_launch_pair_f16(const FmhaLaunch&);
 int fmha_launch_pair_bf16(const FmhaLaunch&);
 
 int fmha_dispatch(int dtype, int p_dtype, int head_dim, const FmhaLaunch& L);
+
+// Checks the arguments of a call and fills the launch (descriptors, parameters, kernel choice) except for
+// FmhaParams::status and the stream.  Returns a cfk status code.
+int fmha_prepare(const struct ::cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype);
 
 }  // namespace cfk

@@ -6,8 +6,6 @@
 // own pool (so even a 256-byte cudaMalloc can fail or fragment), latency-bound loops that cannot take a
 // device-wide synchronisation, and hosts that forbid allocation after start-up.  For them the same kernels run here with the scratch
 // in a fixed array that is part of the library image.  No counterpart in the reference.
-#include <cmath>
-#include <cstring>
 #include <mutex>
 
 #include "fmha_launch.h"
@@ -52,17 +50,6 @@ static int* static_scratch_for_current_device(int* err) {
   return g_static_addr[dev];
 }
 
-static bool packed_or_valid(const int64_t in[3], int64_t out[3], int S, int H, int D, int esz) {
-  if (in[0] == 0 && in[1] == 0 && in[2] == 0) {
-    out[2] = D; out[1] = (int64_t)H * D; out[0] = (int64_t)S * H * D;
-  } else {
-    out[0] = in[0]; out[1] = in[1]; out[2] = in[2];
-  }
-  for (int i = 0; i < 3; ++i)
-    if (out[i] <= 0 || (out[i] * esz) % 16 != 0) return false;
-  return true;
-}
-
 }  // namespace cfk
 
 using namespace cfk;
@@ -79,30 +66,10 @@ using namespace cfk;
 //   * iterations == 0 launches nothing: it waits for `stream` and returns CFK_ERR_DEVICE_WAIT if the status
 //     word left by the preceding call is non-zero (cfk_device_status only sees the allocated block).
 extern "C" int cfk_fmha_forward_static(const cfk_fmha_args* a, cfk_stream_t stream) {
-  if (!a || !a->q || !a->k || !a->v || !a->o) return CFK_ERR_INVALID_ARG;
-  if (a->batch <= 0 || a->heads <= 0 || a->seqlen_q <= 0 || a->seqlen_kv <= 0 || a->iterations < 0)
-    return CFK_ERR_INVALID_ARG;
-  if (a->batch > 65535 || a->heads > 65535) return CFK_ERR_INVALID_ARG;
-  if (!(a->softmax_scale > 0.f) || !std::isfinite(a->softmax_scale)) return CFK_ERR_INVALID_ARG;
-  if (a->dtype != CFK_FP16 && a->dtype != CFK_BF16 && a->dtype != CFK_E4M3) return CFK_ERR_INVALID_ARG;
-  if (a->out_dtype != CFK_FP16 && a->out_dtype != CFK_BF16) return CFK_ERR_INVALID_ARG;
-  if (a->head_dim != 64 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
-  if (a->v_fp16) return CFK_ERR_UNSUPPORTED;   // the hybrid e4m3 / fp16 mode goes through cfk_fmha_forward
-  if (a->dtype == CFK_E4M3 && a->head_dim != 128) return CFK_ERR_UNSUPPORTED;
-  if (a->causal && a->seqlen_kv < a->seqlen_q) return CFK_ERR_UNSUPPORTED;
-  if (a->p_split_keys < -1) return CFK_ERR_INVALID_ARG;
-  const bool fp8 = a->dtype == CFK_E4M3;
-  const float qd = fp8 ? a->q_descale : (a->q_descale == 0.f ? 1.f : a->q_descale);
-  const float kd = fp8 ? a->k_descale : (a->k_descale == 0.f ? 1.f : a->k_descale);
-  const float vd = fp8 ? a->v_descale : (a->v_descale == 0.f ? 1.f : a->v_descale);
-  if (!(qd > 0.f) || !(kd > 0.f) || !(vd > 0.f)) return CFK_ERR_INVALID_ARG;
-  if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->o) & 15u) return CFK_ERR_INVALID_ARG;
-  const int esz = dtype_size(a->dtype);
-  int64_t qs[3], ks[3], vs[3], os[3];
-  if (!packed_or_valid(a->q_stride, qs, a->seqlen_q, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
-  if (!packed_or_valid(a->k_stride, ks, a->seqlen_kv, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
-  if (!packed_or_valid(a->v_stride, vs, a->seqlen_kv, a->heads, a->head_dim, esz)) return CFK_ERR_INVALID_ARG;
-  if (!packed_or_valid(a->o_stride, os, a->seqlen_q, a->heads, a->head_dim, 2)) return CFK_ERR_INVALID_ARG;
+  FmhaLaunch L;
+  int pdt = 0;
+  const int rc = fmha_prepare(a, &L, &pdt);   // host-side only: checks, descriptors, parameters
+  if (rc != CFK_OK) return rc;
 
   if (kFmhaScratchInts > kStaticScratchInts) {
     (void)note_cuda(cudaErrorInvalidValue, "cfk_fmha_forward_static: this build needs more scratch than the static "
@@ -124,42 +91,11 @@ extern "C" int cfk_fmha_forward_static(const cfk_fmha_args* a, cfk_stream_t stre
     return code == 0 ? CFK_OK : CFK_ERR_DEVICE_WAIT;
   }
 
-  FmhaLaunch L;
-  std::memset(&L, 0, sizeof(L));
-  int rc;
-  if ((rc = encode_bshd(&L.tm_q, a->dtype, a->q, a->batch, a->seqlen_q, a->heads, a->head_dim, qs[0], qs[1], qs[2], 128)))
-    return rc;
-  if ((rc = encode_bshd(&L.tm_k, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 128)))
-    return rc;
-  if ((rc = encode_bshd(&L.tm_v, a->dtype, a->v, a->batch, a->seqlen_kv, a->heads, a->head_dim, vs[0], vs[1], vs[2], 128)))
-    return rc;
-  if ((rc = encode_bshd(&L.tm_o, a->out_dtype, a->o, a->batch, a->seqlen_q, a->heads, a->head_dim, os[0], os[1], os[2], 128)))
-    return rc;
-
-  FmhaParams& p = L.p;
-  p.B = a->batch; p.H = a->heads; p.Sq = a->seqlen_q; p.Skv = a->seqlen_kv;
-  p.causal = a->causal ? 1 : 0;
-  p.out_bf16 = a->out_dtype == CFK_BF16;
-  p.nqblk = (a->seqlen_q + 255) / 256;
-  if ((long long)p.nqblk * a->heads * a->batch > 0x7fffffffLL) return CFK_ERR_UNSUPPORTED;
-  p.split_keys = a->dtype == CFK_BF16 ? (a->p_split_keys < 0 ? 1024 : a->p_split_keys) : 0;
-  p.scale_log2 = a->softmax_scale * 1.4426950408889634f * qd * kd;
-  p.out_scale = vd;
-  p.lse = a->lse; p.mi = a->mi; p.sprime = a->sprime;
-  p.s_dump = a->s_dump; p.s_dump_bf16 = a->dtype == CFK_BF16;
-  p.status = status;
-  L.iterations = a->iterations;
+  L.p.status = status;
   L.stream = st;
-  L.exp_emu = cfk_get_tunable(CFK_TUNE_FMHA_EXP_EMU);
-  if (L.exp_emu < 0) L.exp_emu = fp8 ? 2 : 1;
-  const long long kv_bytes = 2LL * a->seqlen_kv * a->head_dim * esz;
-  long long grp = a->causal ? ((long long)cfk_get_tunable(CFK_TUNE_FMHA_GROUP_MB) << 20) / kv_bytes : 1;
-  const long long bh = (long long)a->batch * a->heads;
-  p.group = (int)(grp < 1 ? 1 : (grp > bh ? bh : grp));
-
   // The status word must start at zero: a launch that finds it set does nothing.
   if (note_cuda(cudaMemsetAsync(status, 0, sizeof(int) * kFmhaScratchInts, st), "cudaMemsetAsync(static status)") !=
       cudaSuccess)
     return CFK_ERR_LAUNCH;
-  return fmha_dispatch(a->dtype, a->dtype, a->head_dim, L);
+  return fmha_dispatch(a->dtype, pdt, a->head_dim, L);
 }

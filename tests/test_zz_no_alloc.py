@@ -22,11 +22,11 @@ def _args(lib, low, o, scales, dtype, causal, iterations=1):
                          v_descale=scales[2], iterations=iterations)
 
 
-@pytest.mark.parametrize("dtype,causal", [(0, True), (1, False), (2, False)])
-def test_static_entry_point_matches_the_allocating_one_twice(lib, cuda, dtype, causal):
-    low, _, scales = make_qkv(dtype, 2, 1024, 1024, 3, 128, seed=31 + dtype)
+@pytest.mark.parametrize("dtype,causal,D", [(0, True, 128), (1, False, 128), (2, False, 128), (1, True, 256), (2, True, 64)])
+def test_static_entry_point_matches_the_allocating_one_twice(lib, cuda, dtype, causal, D):
+    low, _, scales = make_qkv(dtype, 2, 1024, 1024, 3, D, seed=31 + dtype)
     low = [x.cuda() for x in low]
-    want = torch.full((2, 1024, 3, 128), -1.0, device="cuda", dtype=torch.float16)
+    want = torch.full((2, 1024, 3, D), -1.0, device="cuda", dtype=torch.float16)
     assert lib.fmha_forward_raw(_args(lib, low, want, scales, dtype, causal)) == 0
     lib.check_device()
     for call in range(2):     # the second call finds the scratch as the first one left it
