@@ -290,3 +290,12 @@ def test_fmha_hybrid_e4m3_qk_fp16_v(lib, oracle, cuda, B, Sq, Skv, H, D, causal)
     cmp = oracle.compare(o.float().cpu().numpy(), ref["o"])
     assert cmp["nonfinite"] == 0 and cmp["max_abs"] <= 2e-3, cmp
     assert np.abs(lse.cpu().numpy() - ref["lse"]).max() <= 2e-3
+
+
+@pytest.mark.parametrize("dtype,D", [(0, 64), (1, 128), (0, 256), (2, 64), (2, 128), (2, 256)])
+@pytest.mark.parametrize("Sq,Skv,causal", [(1, 1, False), (5, 7, True), (130, 3, False), (257, 257, True)])
+def test_fmha_tiny_and_odd_lengths(lib, oracle, cuda, dtype, D, Sq, Skv, causal):
+    """Lengths far below one tile and just past a tile edge: TMA zero-fill, key-tail masking and store clipping."""
+    low, f32, scales = make_qkv(dtype, 2, Sq, Skv, 2, D, seed=97 + Sq + D)
+    got, stats = run_fmha(lib, low, scales, dtype, causal)
+    check(oracle, got, stats, f32, 1.0 / math.sqrt(D), causal, dtype)
