@@ -432,7 +432,8 @@ def main():
             ms2 = e0.elapsed_time(e1) / 10
             tf = flops_of(w2[1], w2[2], w2[3], w2[4], w2[5]) / (ms2 * 1e-3) / 1e12
             others[name] = {"workload": w2[6], "ms": ms2, "tflops": tf, "frac_nominal": tf / NOMINAL[w2[0]],
-                            "frac_measured_bf16_burst": tf / burst}
+                            "frac_measured_bf16_burst": tf / measured_peaks()[0],
+                            "note": "10 back-to-back launches after 3 warm-up launches (burst-like)"}
             del q2, k2, v2, o2
             torch.cuda.empty_cache()
         n = 8192
@@ -449,8 +450,23 @@ def main():
         torch.cuda.synchronize()
         msg = e0.elapsed_time(e1) / 10
         tf = 2.0 * n ** 3 / (msg * 1e-3) / 1e12
+        # burst figure, the way the measured cuBLAS burst peak is taken: best of ten single launches after an idle gap
+        time.sleep(0.3)
+        best = float("inf")
+        for _ in range(10):
+            e0.record(stream)
+            lib.gemm(a, b, c, dtype=cfk_b200.FP16, m=n, n=n, k=n, iterations=1, stream=sptr)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        tf_burst = 2.0 * n ** 3 / (best * 1e-3) / 1e12
+        cublas_burst, cublas_sustained, _ = measured_peaks()
         others["c2"] = {"workload": "gemm fp16 M=N=K=8192, fp32 accumulate, column-major C", "ms": msg, "tflops": tf,
-                        "frac_nominal": tf / 2250.0, "frac_measured_bf16_burst": tf / burst}
+                        "tflops_burst": tf_burst, "frac_nominal": tf / 2250.0,
+                        "frac_measured_bf16_burst": tf_burst / cublas_burst,
+                        "frac_measured_bf16_sustained": tf / cublas_sustained,
+                        "note": "burst = best of 10 single launches after an idle gap, against the cuBLAS burst peak; "
+                                "tflops = 10 back-to-back launches, against the cuBLAS sustained peak"}
         lib.check_device()
         line["other_configs"] = others
 
