@@ -15,7 +15,7 @@
 //
 // The pair halves the B-operand bytes each SM reads from shared memory per FLOP, which is what bounds a
 // single-CTA 128 x 256 tile.  Pairs are persistent (one per two SMs) and walk the tile list in bands of
-// 4 row-tiles so that concurrently running tiles share X and Y panels in L2.  The reference's column-major
+// 8 row-tiles so that concurrently running tiles share X and Y panels in L2.  The reference's column-major
 // C (gemm.cu:388-389) is the row-major D of the swapped problem (X = B, Y = A), so one kernel serves both
 // output orders.
 #include <cuda_bf16.h>
@@ -50,7 +50,7 @@ struct GemmCfg {
   static constexpr int NSTAGE = 6;
   static constexpr int SMEM_BYTES = 1024 + NSTAGE * (XB + YB) + 256;
   static constexpr int NTHREADS = 192;
-  static constexpr int BAND = 4;
+  static constexpr int BAND = 8;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, int& tr, int& tc, int& batch) {
@@ -130,7 +130,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    // UMMA issue: all 32 lanes of the leader's warp run the loop, one elected lane executes the instructions
+    if (rank == 0) {
+      const uint32_t leader = elect_one();
+      const uint32_t peer_delta = map_to_cta(sBar, 1) - sBar;
       constexpr uint32_t idesc_f16 = make_idesc(1, kFmtF16, kFmtF16, 0, 0, C::TILE, C::TILE);
       constexpr uint32_t idesc_bf16 = make_idesc(1, kFmtBF16, kFmtBF16, 0, 0, C::TILE, C::TILE);
       constexpr uint32_t idesc_tf32 = make_idesc(1, 2u, 2u, 0, 0, C::TILE, C::TILE);   // kind::tf32: format code 2
@@ -140,31 +143,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
       for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
         const int buf = local & 1;
         const uint32_t acc_ph = (local >> 1) & 1;
-        if (!mbar_wait(bar_acc_empty + 8 * buf, acc_ph ^ 1u, actx, kErrGemmAccEmpty)) { ok = false; break; }
+        if (!mbar_wait_warp(bar_acc_empty + 8 * buf, acc_ph ^ 1u, actx, kErrGemmAccEmpty)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d = tmem_base + buf * 256;
         for (int kb = 0; kb < nkb; ++kb, ++idx) {
           const int s = idx % C::NSTAGE;
-          if (!mbar_wait(bar_full + 8 * s, (idx / C::NSTAGE) & 1, actx, kErrGemmFull)) { ok = false; break; }
+          if (!mbar_wait_warp(bar_full + 8 * s, (idx / C::NSTAGE) & 1, actx, kErrGemmFull)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t a0 = make_smem_desc(sX + s * C::XB, 16, 1024, kSwizzle128B);
           const uint64_t b0 = make_smem_desc(sY + s * C::YB, 16, 1024, kSwizzle128B);
           if (p.tf32) {
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)   // 32 bytes of reduction per UMMA: 8 tf32 elements
-              umma_ss_pair_tf32(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u);
+              umma_ss_pair_tf32(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc, (kb | kk) != 0 ? 1u : 0u, leader);
           } else {
 #pragma unroll
             for (int kk = 0; kk < C::BK / 16; ++kk)
-              umma_ss_pair<false>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc,
-                                  (kb | kk) != 0 ? 1u : 0u);
+              umma_ss_e<false, true>(d, desc_advance(a0, kk * 32), desc_advance(b0, kk * 32), idesc,
+                                     (kb | kk) != 0 ? 1u : 0u, leader);
           }
-          umma_commit_pair(bar_empty + 8 * s);                  // this CTA's stage
-          umma_commit_pair(map_to_cta(bar_empty + 8 * s, 1));   // the peer's stage
+          umma_commit_e<true>(bar_empty + 8 * s, leader);                // this CTA's stage
+          umma_commit_e<true>(bar_empty + 8 * s + peer_delta, leader);   // the peer's stage
         }
         if (ok) {
-          umma_commit_pair(bar_acc_full + 8 * buf);
-          umma_commit_pair(map_to_cta(bar_acc_full + 8 * buf, 1));
+          umma_commit_e<true>(bar_acc_full + 8 * buf, leader);
+          umma_commit_e<true>(bar_acc_full + 8 * buf + peer_delta, leader);
         }
       }
     }
