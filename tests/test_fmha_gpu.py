@@ -299,3 +299,68 @@ def test_fmha_tiny_and_odd_lengths(lib, oracle, cuda, dtype, D, Sq, Skv, causal)
     low, f32, scales = make_qkv(dtype, 2, Sq, Skv, 2, D, seed=97 + Sq + D)
     got, stats = run_fmha(lib, low, scales, dtype, causal)
     check(oracle, got, stats, f32, 1.0 / math.sqrt(D), causal, dtype)
+
+
+# ---- the benchmark configurations at full size, through size-independent properties -------------------------
+# (the oracle takes minutes at these sizes; a sampled comparison against it is part of bench.py)
+
+FULL_SIZE = [
+    ("c3", 0, 4, 16, 4096, 128, False),
+    ("c4", 1, 2, 32, 8192, 128, True),
+    ("c5", 2, 4, 16, 8192, 128, False),
+]
+
+
+@pytest.mark.parametrize("name,dtype,B,H,S,D,causal", FULL_SIZE)
+def test_fmha_full_size_properties(lib, oracle, cuda, name, dtype, B, H, S, D, causal):
+    """At the sizes the benchmark runs: (1) with V = 1 every output is exactly the normalisation, i.e. 1;
+    (2) O is linear in V (V -> 2 V, a power of two, doubles O to the last bit of a normal fp16); (3) LSE matches the oracle on one
+    sampled (batch, head) slice and the output of that slice meets the tolerance; (4) two runs are bit-identical."""
+    n = B * S * H * D
+    tdt = {0: torch.float16, 1: torch.bfloat16, 2: torch.uint8}[dtype]
+    q, k, v = (torch.empty(B, S, H, D, dtype=tdt, device="cuda") for _ in range(3))
+    scale8 = 6.0 / 448.0
+    for i, t in enumerate((q, k, v)):
+        lib.fill(t, dtype, n, 3081 + i, "normal", scale=(1.0 / scale8 if dtype == 2 else 1.0))
+    desc = [scale8] * 3 if dtype == 2 else [1.0] * 3
+    o = torch.empty(B, S, H, D, dtype=torch.float16, device="cuda")
+    lse = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
+
+    def run(vv, vdesc, out, lse_out=None):
+        lib.fmha_forward(q, k, vv, out, dtype=dtype, batch=B, heads=H, seqlen_q=S, seqlen_kv=S, head_dim=D,
+                         softmax_scale=1.0 / math.sqrt(D), causal=causal, q_descale=desc[0], k_descale=desc[1],
+                         v_descale=vdesc, lse=lse_out)
+        lib.check_device()
+
+    run(v, desc[2], o, lse)
+    o_again = torch.empty_like(o)
+    run(v, desc[2], o_again)
+    assert torch.equal(o, o_again)                                        # (4)
+    o2 = torch.empty_like(o)
+    run(v, 2.0 * desc[2], o2)                                              # doubling V through its de-scale
+    # (2): exact doubling, except where the single output is an fp16 subnormal (one step there is 2^-24)
+    assert float((o2.float() - 2.0 * o.float()).abs().max()) <= 2.0 ** -23
+    ones = torch.empty_like(v)
+    lib.fill(ones, dtype, n, 0, "const", value=1.0)
+    o1 = torch.empty_like(o)
+    run(ones, 1.0, o1)
+    tol1 = 1e-3 if dtype != 2 else 3e-2        # e4m3 P: the row sum is taken before P is rounded, the product after
+    assert float((o1.float() - 1.0).abs().max()) <= tol1                   # (1)
+    # (3) one slice against the oracle
+    b, h = B - 1, H // 2
+    conv = lambda t, s: (lib_to_f32(lib, t[b:b + 1, :, h:h + 1, :].contiguous(), dtype) * s).cpu().numpy()
+    ref = oracle.attention(conv(q, desc[0]), conv(k, desc[1]), conv(v, desc[2]), 1.0 / math.sqrt(D), causal)
+    cmp = oracle.compare(o[b:b + 1, :, h:h + 1, :].float().cpu().numpy(), ref["o"])
+    assert cmp["nonfinite"] == 0
+    if dtype == 2:
+        assert cmp["rel_rms"] <= 3e-2, cmp
+    else:
+        assert cmp["max_abs"] <= 2e-3, cmp
+    assert np.abs(lse[b, h].cpu().numpy() - ref["lse"][0, 0]).max() <= (2e-2 if dtype == 2 else 2e-3)
+
+
+def lib_to_f32(lib, t, dtype):
+    """Device-side conversion of a contiguous tensor of the library's dtype code to float32."""
+    out = torch.empty(t.shape, dtype=torch.float32, device="cuda")
+    lib.convert(t, dtype, out, 3, t.numel())
+    return out
