@@ -77,15 +77,25 @@ __device__ __forceinline__ float2 exp2_pair_sfu(float2 x) { return make_float2(e
 // error (7.5e-5) is below the rounding step of every P format; 2^n by adding n to the exponent bits.
 // The special-function unit delivers 16 results per clock per SM, exactly what the tensor core consumes
 // at D=128, so a share of the exponentials is moved here (packed two-wide FMA instructions).
+// QUAD: a quadratic instead (minimax on [-0.5, 0.5], relative error 1.7e-3) for a P format whose rounding step is
+// far above that (e4m3: 6e-2); one instruction less per pair where the softmax warps are the bound.
+constexpr float kExp2Q0 = 1.00044314f, kExp2Q1 = 0.70344801f, kExp2Q2 = 0.23842894f;
+template <bool QUAD = false>
 __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
   x.x = fmaxf(x.x, -126.f);
   x.y = fmaxf(x.y, -126.f);
   const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));      // 1.5 * 2^23: n sits in the low bits
   const float2 nf = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
   const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
-  float2 q = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
-  q = __ffma2_rn(q, f, make_float2(0.6932609677f, 0.6932609677f));
-  q = __ffma2_rn(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 q;
+  if constexpr (QUAD) {
+    q = __ffma2_rn(make_float2(kExp2Q2, kExp2Q2), f, make_float2(kExp2Q1, kExp2Q1));
+    q = __ffma2_rn(q, f, make_float2(kExp2Q0, kExp2Q0));
+  } else {
+    q = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+    q = __ffma2_rn(q, f, make_float2(0.6932609677f, 0.6932609677f));
+    q = __ffma2_rn(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  }
   q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
   q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
   return q;
@@ -132,7 +142,7 @@ __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t
     for (int j = 0; j < 16; ++j) {
       const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
                                               __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
-      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma<(PT == kDtE4M3)>(x) : exp2_pair_sfu(x);
       if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
     }
     if constexpr (PT == kDtE4M3) {   // 32 probabilities = 8 words = 8 columns
@@ -204,6 +214,7 @@ template <class CFG, int PT, int HD, int EMU>
 __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tO, float sl, bool first,
                                        bool mask_tile, int lim, bool split, uint32_t bar_half, float& m_ref,
                                        float& m_true, float& l) {
+  constexpr bool QUAD = (PT == kDtE4M3);
   // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
   // needs it at all depends only on the tile, so the test costs no vote.
   if (mask_tile) {   // lim: last visible local column of this row
@@ -261,7 +272,7 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
     for (int j = 0; j < 16; ++j) {
       const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
                                               __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
-      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma(x) : exp2_pair_sfu(x);
+      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma<QUAD>(x) : exp2_pair_sfu(x);
       if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
     }
     if constexpr (!SPLIT) {
