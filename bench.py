@@ -83,11 +83,19 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def wait_first(self, limit_s=1.5):
+        """Blocks until nvidia-smi has delivered its first sample (it needs a few hundred ms to start)."""
+        t0 = time.monotonic()
+        while self.proc and not self.lines and time.monotonic() - t0 < limit_s:
+            time.sleep(0.01)
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summary of the samples that arrived between t_begin and t_end (time.monotonic(); a sample is printed
+        up to one interval after it was taken), or of all samples if fewer than three fall inside."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -98,7 +106,12 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for l in self.lines:
+        inside = [l for (t, l) in self.lines
+                  if (t_begin is None or t >= t_begin) and (t_end is None or t <= t_end + 0.03)]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = [l for (_, l) in self.lines], "warm-up and timed region"
+        for l in inside:
             f = [x.strip() for x in l.split(",")]
             if len(f) < 7:
                 continue
@@ -113,7 +126,7 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         sm_sorted = sorted(sm)
         return {"sm_mhz": sm_sorted[len(sm_sorted) // 2], "sm_max_mhz": max(mx), "power_w_max": max(pw),
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "window": window, "reasons": sorted(reasons)}
 
 
 def make_inputs(torch, lib, wl, seed, device):
@@ -268,15 +281,18 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_first()
     barrier()
+    t_begin = time.monotonic()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(args.steps):
         fmha_call(lib, wl, q, k, v, o, scales, lse, stream=sptr)
     e1.record(stream)
     barrier()
+    t_end = time.monotonic()
     ms = e0.elapsed_time(e1) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     lib.check_device()
     t = torch.tensor([ms], dtype=torch.float64, device=device)
     if world > 1:
