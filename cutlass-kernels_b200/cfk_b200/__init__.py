@@ -21,7 +21,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
                 6: "DEVICE_WAIT", 7: "TOO_LARGE"}
 
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
-           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_set_tunable", "cfk_get_tunable"]
+           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_selftest_wait_gives_up", "cfk_set_tunable", "cfk_get_tunable"]
 
 TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL = 0, 1, 2
 
@@ -84,6 +84,7 @@ class CfkLib:
         L.cfk_last_cuda_error.restype = C.c_char_p
         L.cfk_selftest_umma.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 8 + [C.c_void_p]
         L.cfk_umma_peak.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p]
+        L.cfk_selftest_wait_gives_up.argtypes = [C.c_int, C.c_void_p]
 
     # -- raw calls (return the status code) ---------------------------------------------------
     def fmha_forward_raw(self, args: FmhaArgs, stream=None) -> int:
@@ -155,6 +156,10 @@ class CfkLib:
                       stream=None) -> int:
         return int(self.lib.cfk_selftest_umma(_ptr(a), _ptr(b), _ptr(d), n, a_fmt, b_fmt, int(b_mn_major),
                                               int(a_from_tmem), lbo, sbo, step, stream))
+
+    def selftest_wait_gives_up(self, limit_ms: int, stream=None) -> int:
+        """Enqueues one warp whose bounded wait runs out after `limit_ms`; returns the status code of the launch."""
+        return int(self.lib.cfk_selftest_wait_gives_up(limit_ms, stream))
 
     def device_status(self):
         """(return code, device status word); synchronises the device and clears the word."""

@@ -64,7 +64,8 @@ struct AbortCtx {
 };
 
 // Returns false if the wait was abandoned (time limit, or another role of this CTA aborted).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
@@ -74,7 +75,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
       if (*ctx.cta_abort) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > limit_ns) {
         *ctx.cta_abort = 1u;
         atomicCAS(ctx.status, kDevOk, where);
         return false;

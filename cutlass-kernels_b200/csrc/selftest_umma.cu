@@ -266,3 +266,34 @@ extern "C" int cfk_umma_peak(int dtype, int groups, double* flops_out, cfk_strea
   *flops_out = (double)sms * groups * 4.0 * 2.0 * 128 * 256 * (32 / dtype_size(dtype));
   return note_cuda(cudaGetLastError(), "umma peak launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
 }
+
+// ---- the bounded wait, exercised on purpose ---------------------------------------------------------------
+// One warp waits on an mbarrier that nothing ever arrives on, through the same mbar_wait the kernels use but
+// with a limit of `limit_ns`.  The wait gives up, writes kErrSelftestWait into the status word and the kernel
+// returns normally: no trap, no fault, the context stays usable.
+namespace cfk {
+constexpr int kErrSelftestWait = 901;
+
+__global__ void __launch_bounds__(32, 1) wait_gives_up_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t s_bar;
+  __shared__ uint32_t s_abort;
+  const uint32_t bar = smem_u32(&s_bar);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    s_abort = 0u;
+    fence_barrier_init();
+  }
+  __syncwarp();
+  const AbortCtx actx{&s_abort, status};
+  (void)mbar_wait(bar, 0, actx, kErrSelftestWait, limit_ns);
+}
+}  // namespace cfk
+
+extern "C" int cfk_selftest_wait_gives_up(int limit_ms, cfk_stream_t stream) {
+  if (limit_ms < 1 || limit_ms > 1000) return CFK_ERR_INVALID_ARG;
+  int err = CFK_OK;
+  int* status = device_status_block(&err);
+  if (!status) return err;
+  wait_gives_up_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)limit_ms * 1000000ull);
+  return note_cuda(cudaGetLastError(), "wait selftest launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+}

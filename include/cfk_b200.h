@@ -185,6 +185,15 @@ int cfk_version(void);
 int cfk_umma_peak(int dtype, int groups, double* flops_out, cfk_stream_t stream);
 
 /*
+ * Failure-path self-test: launches one warp that waits, through the kernels' own bounded wait with a limit of
+ * `limit_ms` (1..1000), on a barrier nothing arrives on.  The wait gives up and records code 901 in the status
+ * word; cfk_device_status then returns CFK_ERR_DEVICE_WAIT with that code, and FMHA / GEMM launches enqueued
+ * before the word is read do nothing.  Nothing traps or faults.  No counterpart in the reference, whose kernels
+ * wait without a limit.
+ */
+int cfk_selftest_wait_gives_up(int limit_ms, cfk_stream_t stream);
+
+/*
  * Single-CTA UMMA self-test used by the GPU test-suite to prove each operand-descriptor form
  * (K-major / MN-major shared-memory operands, A from tensor memory, 16-bit and e4m3 kinds) against
  * a CPU product.  D[128][n] (fp32, row-major) = A[128][k] * B, where B is [n][k] (b_mn_major = 0)
