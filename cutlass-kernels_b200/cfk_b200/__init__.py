@@ -23,7 +23,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
            "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_selftest_wait_gives_up", "cfk_set_tunable", "cfk_get_tunable"]
 
-TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL = 0, 1, 2
+TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL, TUNE_FMHA_GRID = 0, 1, 2, 3
 
 
 class FmhaArgs(C.Structure):
@@ -82,7 +82,7 @@ class CfkLib:
         L.cfk_convert.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_void_p]
         L.cfk_device_status.argtypes = [C.POINTER(C.c_int)]
         L.cfk_last_cuda_error.restype = C.c_char_p
-        L.cfk_selftest_umma.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 8 + [C.c_void_p]
+        L.cfk_selftest_umma.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
         L.cfk_umma_peak.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p]
         L.cfk_selftest_wait_gives_up.argtypes = [C.c_int, C.c_void_p]
 
@@ -152,10 +152,9 @@ class CfkLib:
             raise CfkError(rc, self.last_error())
         return float(flops.value)
 
-    def selftest_umma(self, a, b, d, n, a_fmt, b_fmt, b_mn_major, a_from_tmem, lbo=-1, sbo=-1, step=-1,
-                      stream=None) -> int:
+    def selftest_umma(self, a, b, d, n, a_fmt, b_fmt, b_mn_major, a_from_tmem, stream=None) -> int:
         return int(self.lib.cfk_selftest_umma(_ptr(a), _ptr(b), _ptr(d), n, a_fmt, b_fmt, int(b_mn_major),
-                                              int(a_from_tmem), lbo, sbo, step, stream))
+                                              int(a_from_tmem), stream))
 
     def selftest_wait_gives_up(self, limit_ms: int, stream=None) -> int:
         """Enqueues one warp whose bounded wait runs out after `limit_ms`; returns the status code of the launch."""

@@ -6,6 +6,7 @@
 
 #include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -160,8 +161,22 @@ __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, int
 
 // Tunables (process-wide).  Defaults are the measured best on B200.
 // EXP_EMU -1 = by type: 1 of 4 pairs for 16-bit inputs, 2 of 4 for e4m3 (measured best on B200).
-static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64, 0};
-static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}, {0}};
+static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64, 0, 0};
+static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}, {0}, {0}};
+
+// The knobs can also be set from the environment (CFK_TUNE_FMHA_EXP_EMU, CFK_TUNE_FMHA_GROUP_MB, CFK_TUNE_FMHA_KERNEL,
+// CFK_TUNE_FMHA_GRID), read once before the first FMHA call: the command-line drivers have no flags for them.
+static void tunables_from_env() {
+  static std::once_flag once;
+  std::call_once(once, [] {
+    static const char* const names[CFK_TUNE_COUNT] = {"CFK_TUNE_FMHA_EXP_EMU", "CFK_TUNE_FMHA_GROUP_MB",
+                                                      "CFK_TUNE_FMHA_KERNEL", "CFK_TUNE_FMHA_GRID"};
+    for (int i = 0; i < CFK_TUNE_COUNT; ++i) {
+      const char* v = std::getenv(names[i]);
+      if (v && *v) (void)cfk_set_tunable(i, std::atoi(v));
+    }
+  });
+}
 
 static bool valid_dtype(int dt) { return dt >= CFK_FP16 && dt <= CFK_FP32; }
 
@@ -176,7 +191,7 @@ extern "C" int cfk_set_tunable(int which, int value) {
   if (value < 0) value = kTunableDefault[which];
   if (which == CFK_TUNE_FMHA_EXP_EMU && value > 3) return CFK_ERR_INVALID_ARG;
   if (which == CFK_TUNE_FMHA_GROUP_MB && (value < 1 || value > 1024)) return CFK_ERR_INVALID_ARG;
-  if (which == CFK_TUNE_FMHA_KERNEL && value > 1) return CFK_ERR_INVALID_ARG;
+  if (which == CFK_TUNE_FMHA_KERNEL && value > 2) return CFK_ERR_INVALID_ARG;
   g_tunable[which].store(value);
   return CFK_OK;
 }
@@ -270,6 +285,7 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   if (!resolve_strides(a->v_stride, vs, a->seqlen_kv, a->heads, a->head_dim, dtype_size(vdt))) return CFK_ERR_INVALID_ARG;
   if (!resolve_strides(a->o_stride, os, a->seqlen_q, a->heads, a->head_dim, 2)) return CFK_ERR_INVALID_ARG;
 
+  tunables_from_env();
   FmhaLaunch& L = *out;
   std::memset(&L, 0, sizeof(L));
   int rc;
@@ -286,6 +302,8 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
 
   L.variant = g_tunable[CFK_TUNE_FMHA_KERNEL].load();
   if (L.variant == 1 && (a->dtype == CFK_E4M3 || a->head_dim != 128)) L.variant = 0;
+  if (a->head_dim == 256) L.variant = 0;
+  L.grid_ctas = g_tunable[CFK_TUNE_FMHA_GRID].load();
   if (L.variant == 1) {   // CTA-pair kernel: each CTA loads 64 keys of a K tile and one 64-column span of a V tile
     if ((rc = encode_bshd(&L.tm_k_half, a->dtype, a->k, a->batch, a->seqlen_kv, a->heads, a->head_dim, ks[0], ks[1], ks[2], 64)))
       return rc;
@@ -297,7 +315,8 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   p.B = a->batch; p.H = a->heads; p.Sq = a->seqlen_q; p.Skv = a->seqlen_kv;
   p.causal = a->causal ? 1 : 0;
   p.out_bf16 = a->out_dtype == CFK_BF16;
-  p.nqblk = a->head_dim == 256 ? (a->seqlen_q + 127) / 128 : (a->seqlen_q + 255) / 256;   // hd 256: one tile per CTA
+  // one 128-row tile per CTA at head dimension 256 and in the persistent kernel, two side by side otherwise
+  p.nqblk = (a->head_dim == 256 || L.variant == 2) ? (a->seqlen_q + 127) / 128 : (a->seqlen_q + 255) / 256;
   p.split_keys = a->dtype == CFK_BF16 ? (a->p_split_keys < 0 ? 1024 : a->p_split_keys) : 0;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f * qd * kd;
   p.out_scale = vd;

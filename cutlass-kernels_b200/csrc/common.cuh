@@ -57,6 +57,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// Non-blocking form: true if the phase of the given parity has completed.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 
 struct AbortCtx {
   volatile uint32_t* cta_abort;  // shared memory flag
@@ -64,13 +76,17 @@ struct AbortCtx {
 };
 
 // Returns false if the wait was abandoned (time limit, or another role of this CTA aborted).
+// `backoff_ns` > 0: sleep that long between looks.  For roles that wait long and are in no hurry (an epilogue waiting
+// for its item to end, a producer waiting for a free slot): a warp that polls takes issue slots from the warps of its
+// scheduler that are computing.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where,
-                                          unsigned long long limit_ns = kWaitLimitNs) {
+                                          unsigned long long limit_ns = kWaitLimitNs, unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((++spins & 0xffu) == 0) {
       if (*ctx.cta_abort) return false;
       const unsigned long long now = globaltimer_ns();
@@ -84,8 +100,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
   }
 }
 // Same, with a warp-uniform verdict (needed before warp-collective tcgen05.ld/st).
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where) {
-  const bool ok = mbar_wait(bar, parity, ctx, where);
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where,
+                                               unsigned backoff_ns = 0) {
+  const bool ok = mbar_wait(bar, parity, ctx, where, kWaitLimitNs, backoff_ns);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -159,6 +176,15 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 #include "tmem_ldst.inc"
+// One 32-bit column of this thread's TMEM lane (warp-collective): per-row scalars that travel between roles.
+__device__ __forceinline__ void tmem_st_x1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tmem_ld_x1(uint32_t taddr) {
+  uint32_t v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(taddr));
+  return v;
+}
 
 // ---- UMMA descriptors -----------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit): start address, leading/stride byte offsets (all >> 4),

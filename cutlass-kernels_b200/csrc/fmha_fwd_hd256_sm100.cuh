@@ -47,8 +47,8 @@ struct FmhaHd256Cfg {
   static constexpr uint32_t IDESC_QK = make_idesc(1, FMT, FMT, 0, 0, 128, 128);
   static constexpr uint32_t IDESC_PV = make_idesc(1, FMT, FMT, 0, 1, 128, 128);
   static constexpr int NTHREADS = 192;
-  static constexpr float TAU = (DT == kDtE4M3) ? 2.0f : 8.0f;
-  static constexpr float PSHIFT = (DT == kDtE4M3) ? 6.0f : 0.0f;
+  static constexpr float TAU = (DT == kDtE4M3) ? 4.0f : 8.0f;      // see FmhaCfg
+  static constexpr float PSHIFT = (DT == kDtE4M3) ? 4.0f : 0.0f;
 };
 
 // tm_q / tm_o: boxes of 128 rows x all 128-byte spans of a row; tm_k / tm_v: 128 keys x 128 columns (HSPANS spans).

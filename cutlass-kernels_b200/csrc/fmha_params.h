@@ -7,13 +7,15 @@ constexpr int kDtF16 = 0, kDtBF16 = 1, kDtE4M3 = 2;
 
 // Where a bounded wait gave up (stored in the status word).
 constexpr int kErrFmhaQFull = 101, kErrFmhaKvFull = 102, kErrFmhaKvEmpty = 103, kErrFmhaSFull = 104,
-              kErrFmhaPFull = 105, kErrFmhaOFull = 106, kErrFmhaOStaged = 107;
+              kErrFmhaPFull = 105, kErrFmhaOFull = 106, kErrFmhaOStaged = 107, kErrFmhaRowMax = 112,
+              kErrFmhaCorrReq = 113, kErrFmhaCorrDone = 114, kErrFmhaOFree = 115, kErrFmhaQFree = 116,
+              kErrFmhaStats = 117, kErrFmhaCorrPv = 118;
 
 struct FmhaParams {
   int B, H, Sq, Skv;
   int causal;        // key j visible to query i iff j <= i + (Skv - Sq)
   int out_bf16;      // output element type: 0 fp16, 1 bf16
-  int nqblk;         // number of 256-row query blocks
+  int nqblk;         // number of query blocks (256 rows each; 128 for the kernels with one query tile per CTA)
   int group;         // (batch, head) pairs scheduled side by side (their K and V share L2)
   int split_keys;    // bf16: CTAs whose first row sees fewer keys than this keep P as hi + lo (0 = never)
   float scale_log2;  // softmax_scale * log2(e) * q_descale * k_descale

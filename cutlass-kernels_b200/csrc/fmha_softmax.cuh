@@ -66,9 +66,12 @@ struct FmhaCfg {
   static constexpr int LAUNCH_REGS = 168, SOFTMAX_REGS = 216, AUX_REGS = 72;
   static_assert(2 * 128 * SOFTMAX_REGS + 128 * AUX_REGS <= NTHREADS * LAUNCH_REGS, "setmaxnreg would block forever");
   // log2-domain slack before the running maximum is moved, and a constant exponent offset that puts
-  // P into the well-represented range of its type (it cancels in O / l).
-  static constexpr float TAU = (PT == kDtE4M3) ? 2.0f : 8.0f;
-  static constexpr float PSHIFT = (PT == kDtE4M3) ? 6.0f : 0.0f;
+  // P into the well-represented range of its type (it cancels in O / l).  For e4m3 the two share the head-room
+  // below the format's largest value (448): 2^(PSHIFT + TAU) = 256.  An even split moves the maximum far less
+  // often than PSHIFT = 6, TAU = 2 did (then one row group in six asked for a rescale on N(0,1) inputs), and values
+  // down to 2^-10 of the row's reference maximum still fall into the normal range of the format.
+  static constexpr float TAU = (PT == kDtE4M3) ? 4.0f : 8.0f;
+  static constexpr float PSHIFT = (PT == kDtE4M3) ? 4.0f : 0.0f;
 };
 
 // exp2 of a pair of log2-domain scores on the special-function unit ...
@@ -114,29 +117,31 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
 #define CFK_PROF_FLUSH(base, n, cond)
 #endif
 
-// Row maximum of the 128 scores a thread holds: sixteen independent chains, then a tree.
-__device__ __forceinline__ float row_max128(const uint32_t (&sreg)[128]) {
+// Row maximum of the N scores a thread holds: sixteen independent chains, then a tree.
+template <int N>
+__device__ __forceinline__ float row_max_n(const uint32_t (&sreg)[N]) {
   float mx[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) mx[i] = __uint_as_float(sreg[i]);
 #pragma unroll
-  for (int i = 16; i < 128; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
+  for (int i = 16; i < N; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
 #pragma unroll
   for (int w = 8; w >= 1; w >>= 1)
 #pragma unroll
     for (int i = 0; i < w; ++i) mx[i] = fmaxf(mx[i], mx[i + w]);
   return mx[0];
 }
+__device__ __forceinline__ float row_max128(const uint32_t (&sreg)[128]) { return row_max_n<128>(sreg); }
 
-// P = 2^(s * sl + negm) for the 128 scores of a row, rounded to the operand type and stored to tensor memory at
-// tP (64 columns, 32 for e4m3); with SPLIT (bf16) the rounding remainder goes to tLo as a second bf16 term.  Returns
-// the row sum.
-template <int PT, int EMU, bool SPLIT>
-__device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t tP, uint32_t tLo, float sl, float negm) {
+// P = 2^(s * sl + negm) for the N scores a thread holds of a row (N = 128: the whole key tile; 64: one half of it),
+// rounded to the operand type and stored to tensor memory at tP (N/2 columns, N/4 for e4m3); with SPLIT (bf16) the
+// rounding remainder goes to tLo as a second bf16 term.  Returns the sum of the N probabilities.
+template <int N, int PT, int EMU, bool SPLIT>
+__device__ __forceinline__ float emit_p(const uint32_t (&sreg)[N], uint32_t tP, uint32_t tLo, float sl, float negm) {
   const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int c = 0; c < N / 32; ++c) {
     float2 pr[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -168,6 +173,10 @@ __device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t
     }
   }
   return (acc0.x + acc0.y) + (acc1.x + acc1.y);
+}
+template <int PT, int EMU, bool SPLIT>
+__device__ __forceinline__ float emit_p128(const uint32_t (&sreg)[128], uint32_t tP, uint32_t tLo, float sl, float negm) {
+  return emit_p<128, PT, EMU, SPLIT>(sreg, tP, tLo, sl, negm);
 }
 
 // Debugging only: the `n` raw scores of query row `row_g` against keys key0 .. key0+n-1 (held by the calling thread,

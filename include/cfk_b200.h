@@ -166,9 +166,13 @@ const char* cfk_last_cuda_error(void);
  *                           this many MiB (so they share L2), heaviest query blocks first.
  *   CFK_TUNE_FMHA_KERNEL    which FMHA kernel runs: 0 one CTA per 256 query rows (two 128-row tiles side by side);
  *                           1 pairs of CTAs (two SMs per 256 rows, tcgen05 cta_group::2; 16-bit inputs with head
- *                           dimension 128 only, other shapes run kernel 0).
+ *                           dimension 128 only, other shapes run kernel 0); 2 a persistent grid whose CTAs take one
+ *                           128-row tile at a time, with the scores double-buffered, both softmax warpgroups on the
+ *                           two halves of the same key tile and a correction warpgroup (head dimensions 64 and 128).
+ *   CFK_TUNE_FMHA_GRID      kernel 2: CTAs of the persistent grid; 0 = one per SM.  Never more than work items.
  */
-enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_FMHA_KERNEL = 2, CFK_TUNE_COUNT = 3 };
+enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_FMHA_KERNEL = 2, CFK_TUNE_FMHA_GRID = 3,
+                   CFK_TUNE_COUNT = 4 };
 int cfk_set_tunable(int which, int value);
 int cfk_get_tunable(int which); /* -1 for an unknown knob */
 
@@ -198,11 +202,13 @@ int cfk_selftest_wait_gives_up(int limit_ms, cfk_stream_t stream);
  * (K-major / MN-major shared-memory operands, A from tensor memory, 16-bit and e4m3 kinds) against
  * a CPU product.  D[128][n] (fp32, row-major) = A[128][k] * B, where B is [n][k] (b_mn_major = 0)
  * or [k][n] (b_mn_major = 1).  k * elem_size must be 128; n is 64 or 128.  a_from_tmem routes A
- * through tensor memory.  a_fmt / b_fmt are cfk_dtype codes.  lbo / sbo / step override the
- * descriptor fields of B when non-negative.  No counterpart in the reference.
+ * through tensor memory.  a_fmt / b_fmt are cfk_dtype codes and must be equal: one MMA instruction
+ * takes both operands in one format, and a mixed pair is refused with CFK_ERR_UNSUPPORTED before any
+ * launch.  The descriptor fields of B are the ones the kernels use; the caller cannot override them.
+ * No counterpart in the reference.
  */
 int cfk_selftest_umma(const void* a, const void* b, float* d, int n, int a_fmt, int b_fmt, int b_mn_major,
-                      int a_from_tmem, int lbo, int sbo, int step, cfk_stream_t stream);
+                      int a_from_tmem, cfk_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -116,21 +116,42 @@ void fmhaForwardDeviceLoop(int SEQLEN, int KEYLEN, int NUMHEADS, int BATCH, Prec
                                                                           miOut, sPrimeOut, iterations, scale, stream);
     return;
   }
-  // Batch is the outermost dimension, so a batch slice is a plain pointer offset (fmha_forward.cu:406-411).
+  // Batch is the outermost dimension, so a batch slice is a plain pointer offset (fmha_forward.cu:406-411), the
+  // debug score tensor S included (offsetS there).  The slice streams are created like the reference's
+  // (cudaStreamCreate, fmha_forward.cu:403-404), so work on them is ordered against the legacy default stream; in
+  // addition every slice stream waits on an event recorded on `stream` and `stream` waits on each slice's end, so
+  // that events or kernels a caller puts on `stream` around this call bracket all slices whatever `stream` is.
   const int b = BATCH / nStreams;
   const size_t q_el = (size_t)b * SEQLEN * NUMHEADS * HEADDIM, kv_el = (size_t)b * KEYLEN * NUMHEADS * HEADDIM;
   const size_t st_el = (size_t)b * NUMHEADS * SEQLEN;
+  const size_t s_el = (size_t)b * NUMHEADS * SEQLEN * KEYLEN;
+  cudaEvent_t fork = nullptr;
+  if (cudaEventCreateWithFlags(&fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventRecord(fork, stream) != cudaSuccess) {
+    if (fork) cudaEventDestroy(fork);
+    cfk::note_status("fmhaForwardDeviceLoop", CFK_ERR_LAUNCH);
+    return;
+  }
   for (int i = 0; i < nStreams; ++i) {
-    cudaStream_t s;
-    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaStream_t s = nullptr;
+    cudaEvent_t join = nullptr;
+    if (cudaStreamCreate(&s) != cudaSuccess || cudaEventCreateWithFlags(&join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaStreamWaitEvent(s, fork, 0) != cudaSuccess) {
+      if (s) cudaStreamDestroy(s);
+      if (join) cudaEventDestroy(join);
       cfk::note_status("fmhaForwardDeviceLoop", CFK_ERR_LAUNCH);
-      return;
+      break;
     }
     fmhaForwardDevice<PrecType, Gemm2Type, SoftType, OutputType, HEADDIM>(
-        SEQLEN, KEYLEN, NUMHEADS, b, Q + i * q_el, K + i * kv_el, V + i * kv_el, S, O + i * q_el,
-        miOut ? miOut + i * st_el : nullptr, sPrimeOut ? sPrimeOut + i * st_el : nullptr, iterations, scale, s);
-    cudaStreamDestroy(s);   // destruction is deferred until the enqueued work has finished
+        SEQLEN, KEYLEN, NUMHEADS, b, Q + i * q_el, K + i * kv_el, V + i * kv_el, S ? S + i * s_el : nullptr,
+        O + i * q_el, miOut ? miOut + i * st_el : nullptr, sPrimeOut ? sPrimeOut + i * st_el : nullptr, iterations,
+        scale, s);
+    if (cudaEventRecord(join, s) != cudaSuccess || cudaStreamWaitEvent(stream, join, 0) != cudaSuccess)
+      cfk::note_status("fmhaForwardDeviceLoop", CFK_ERR_LAUNCH);
+    cudaEventDestroy(join);   // released once the event has completed
+    cudaStreamDestroy(s);     // destruction is deferred until the enqueued work has finished
   }
+  cudaEventDestroy(fork);
 }
 
 template <typename TA, typename TB, typename TC, typename Alpha, typename Beta>

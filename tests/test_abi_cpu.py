@@ -81,3 +81,21 @@ def test_fill_and_convert_reject_bad_arguments(lib):
     assert lib.lib.cfk_fill(None, 0, 10, 1, 0, 0, 1.0, 0.0, None) == 1
     assert lib.lib.cfk_fill(0x1000, 9, 10, 1, 0, 0, 1.0, 0.0, None) == 1
     assert lib.lib.cfk_convert(0x1000, 0, None, 1, 10, 1.0, None) == 1
+
+
+@pytest.mark.parametrize("a_fmt,b_fmt", [(cfk_b200.FP16, cfk_b200.BF16), (cfk_b200.BF16, cfk_b200.FP16),
+                                         (cfk_b200.FP16, cfk_b200.E4M3), (cfk_b200.E4M3, cfk_b200.BF16)])
+@pytest.mark.parametrize("a_from_tmem", [0, 1])
+def test_selftest_umma_refuses_mixed_operand_formats_before_any_launch(lib, a_fmt, b_fmt, a_from_tmem):
+    """One MMA instruction takes A and B in one format; a mixed pair faults the tensor core, so the entry point
+    refuses it on the host (this box has no device: a launch attempt would return a different code)."""
+    assert lib.selftest_umma(0x1000, 0x2000, 0x3000, 128, a_fmt, b_fmt, 0, a_from_tmem) == 2
+
+
+def test_selftest_umma_takes_no_descriptor_overrides(lib):
+    """The descriptor fields of B are fixed to what the kernels use: the entry point has no parameter for them."""
+    assert len(lib.lib.cfk_selftest_umma.argtypes) == 9
+    text = open(os.path.join(ROOT, "include", "cfk_b200.h")).read()
+    decl = text[text.index("int cfk_selftest_umma("):]
+    decl = decl[:decl.index(";")]
+    assert "lbo" not in decl and "sbo" not in decl and "step" not in decl

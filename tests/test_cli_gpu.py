@@ -39,6 +39,21 @@ def test_fmha_forward_cli_verify_all_and_streams(cuda):
         assert line in text, text
 
 
+def test_fmha_forward_cli_times_the_work_of_every_stream(cuda):
+    """The CUTE_FMHA line is taken from events on stream 0 around fmhaForwardDeviceLoop; with the batch split over two
+    streams those events must still bracket all the work (the reference's cudaStreamCreate streams order themselves
+    against stream 0), not just the time to enqueue it."""
+    import re
+    ms = {}
+    for streams in (1, 2):
+        rc, text = run("fmha_forward", "--batch-size=4", "--dim-size=2048", "--head-size=128", "--seq-length=4096",
+                       "--iterations=5", "--prec-type=1", f"--num-cuda-streams={streams}")
+        assert rc == 0, text
+        ms[streams] = float(re.search(r"CUTE_FMHA:.*\(\s*([0-9.]+)\)ms", text).group(1))
+    assert ms[1] > 0.2                          # 2.7e11 flop cannot take less on any B200
+    assert 0.5 * ms[1] <= ms[2] <= 2.0 * ms[1], ms
+
+
 def test_fmha_forward_cli_hybrid_fp8_and_causal(cuda):
     rc, text = run("fmha_forward", "--batch-size=1", "--dim-size=256", "--head-size=128", "--seq-length=1024",
                    "--iterations=2", "--prec-type=2", "--hybrid-fp8=true", "--reference-check=true")
