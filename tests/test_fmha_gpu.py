@@ -137,6 +137,39 @@ def test_fmha_head_range_shard_with_strides(lib, oracle, cuda):
     assert (o[:, :, :h0] == -1).all() and (o[:, :, h1:] == -1).all()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fmha_shard_plan_union_is_bit_identical_to_the_unsharded_launch(lib, cuda, world):
+    """The multi-GPU split on one device: every rank's sub-calls (cfk_b200.sharding.sub_calls, launched the way
+    bench.py launches them: pointer offset + the unsharded strides) write their slices of one output tensor; the
+    union equals the single unsharded launch bit for bit, LSE included, and nothing else is written."""
+    import bench
+    B, S, H, D = 2, 640, 6, 128
+    wl = (1, B, H, S, D, True, "shard test")
+    q, k, v = (torch.empty(B, S, H, D, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    for i, t in enumerate((q, k, v)):
+        lib.fill(t, 1, t.numel(), 3081 + i, "normal")
+    o_full = torch.full((B, S, H, D), -1.0, dtype=torch.float16, device="cuda")
+    lse_full = torch.full((B, H, S), -1.0, dtype=torch.float32, device="cuda")
+    assert bench.run_plan(lib, wl, bench.shard_plan(B, H, 1, 0), q, k, v, o_full, [1, 1, 1], lse_full) == 1
+    lib.check_device()
+    o = torch.full((B, S, H, D), -1.0, dtype=torch.float16, device="cuda")
+    lse = torch.full((B, H, S), -1.0, dtype=torch.float32, device="cuda")
+    done = torch.zeros(B, H, dtype=torch.bool)
+    for rank in range(world):
+        plan = bench.shard_plan(B, H, world, rank)
+        bench.run_plan(lib, wl, plan, q, k, v, o, [1, 1, 1], lse)
+        lib.check_device()
+        for c in plan:
+            done[c.batch_begin:c.batch_begin + c.batch_count, c.head_begin:c.head_begin + c.head_count] = True
+        # what the ranks so far have not been given is still untouched
+        for b in range(B):
+            for h in range(H):
+                if not done[b, h]:
+                    assert bool((o[b, :, h, :] == -1).all()) and bool((lse[b, h] == -1).all())
+    assert bool(done.all())
+    assert torch.equal(o, o_full) and torch.equal(lse, lse_full)
+
+
 def test_fmha_is_deterministic_and_iterations_repeat(lib, cuda):
     low, _, scales = make_qkv(0, 1, 1024, 1024, 2, 128, seed=2)
     a, _ = run_fmha(lib, low, scales, 0, True, want_stats=False)
