@@ -21,7 +21,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
                 6: "DEVICE_WAIT", 7: "TOO_LARGE"}
 
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
-           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_selftest_wait_gives_up", "cfk_set_tunable", "cfk_get_tunable"]
+           "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_selftest_wait_gives_up", "cfk_selftest_wait_gives_up_static", "cfk_set_tunable", "cfk_get_tunable"]
 
 TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL, TUNE_FMHA_GRID = 0, 1, 2, 3
 
@@ -85,6 +85,7 @@ class CfkLib:
         L.cfk_selftest_umma.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int] * 5 + [C.c_void_p]
         L.cfk_umma_peak.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_double), C.c_void_p]
         L.cfk_selftest_wait_gives_up.argtypes = [C.c_int, C.c_void_p]
+        L.cfk_selftest_wait_gives_up_static.argtypes = [C.c_int, C.c_void_p]
 
     # -- raw calls (return the status code) ---------------------------------------------------
     def fmha_forward_raw(self, args: FmhaArgs, stream=None) -> int:
@@ -159,6 +160,10 @@ class CfkLib:
     def selftest_wait_gives_up(self, limit_ms: int, stream=None) -> int:
         """Enqueues one warp whose bounded wait runs out after `limit_ms`; returns the status code of the launch."""
         return int(self.lib.cfk_selftest_wait_gives_up(limit_ms, stream))
+
+    def selftest_wait_gives_up_static(self, limit_ms: int, stream=None) -> int:
+        """The same wait, reporting into the fixed scratch array of cfk_fmha_forward_static."""
+        return int(self.lib.cfk_selftest_wait_gives_up_static(limit_ms, stream))
 
     def device_status(self):
         """(return code, device status word); synchronises the device and clears the word."""

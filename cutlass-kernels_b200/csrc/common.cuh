@@ -341,6 +341,22 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The skip decision of a CTA pair (see cta_should_skip), taken ONCE for the pair: if each CTA read the status word
+// for itself, another CTA's wait could give up between the two reads, one CTA of the pair would return and its peer
+// would go on to allocate tensor memory for the pair (which has no time limit) and to signal barriers in the shared
+// memory of a CTA that is gone.  Rank 0 reads the word and stores the verdict into both CTAs' shared memory; after
+// the cluster barrier both branch on their own copy.  Every thread of both CTAs must call this.
+__device__ __forceinline__ bool pair_should_skip(const int* status) {
+  __shared__ uint32_t s_pair_skip;
+  if (threadIdx.x == 0 && cluster_ctarank() == 0) {
+    const uint32_t v = (uint32_t)(*reinterpret_cast<const volatile int*>(status) != 0);
+    const uint32_t here = smem_u32(&s_pair_skip);
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(here, 0)), "r"(v) : "memory");
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(map_to_cta(here, 1)), "r"(v) : "memory");
+  }
+  cluster_sync_all();   // release / acquire at cluster scope: the peer's copy is written before anyone reads
+  return *reinterpret_cast<volatile uint32_t*>(&s_pair_skip) != 0u;
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }

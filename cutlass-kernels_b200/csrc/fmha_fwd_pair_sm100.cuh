@@ -131,7 +131,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int n_kv = max(tiles_for(qblk * 256), tiles_for(qblk * 256 + 128));
   const int row0 = qblk * 256 + (int)rank * 128;
 
-  if (cta_should_skip(p.status)) return;   // both CTAs of a pair read the same word
+  if (pair_should_skip(p.status)) return;   // one decision for the pair: both CTAs skip or both run
 
   if (tid == 0) {
     mbar_init(bar_q_full, 2);

@@ -136,8 +136,12 @@ __device__ __forceinline__ float row_max128(const uint32_t (&sreg)[128]) { retur
 // P = 2^(s * sl + negm) for the N scores a thread holds of a row (N = 128: the whole key tile; 64: one half of it),
 // rounded to the operand type and stored to tensor memory at tP (N/2 columns, N/4 for e4m3); with SPLIT (bf16) the
 // rounding remainder goes to tLo as a second bf16 term.  Returns the sum of the N probabilities.
-template <int N, int PT, int EMU, bool SPLIT>
-__device__ __forceinline__ float emit_p(const uint32_t (&sreg)[N], uint32_t tP, uint32_t tLo, float sl, float negm) {
+// With HALF_ARRIVE the first half of P is released on its own: once its stores have had the time of the next
+// chunk's exponentials to land, the warp arrives on `bar_half`, and the UMMA thread starts P V on those keys while the
+// second half is still being computed.
+template <int N, int PT, int EMU, bool SPLIT, bool HALF_ARRIVE = false>
+__device__ __forceinline__ float emit_p(const uint32_t (&sreg)[N], uint32_t tP, uint32_t tLo, float sl, float negm,
+                                        uint32_t bar_half = 0u) {
   const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -149,6 +153,13 @@ __device__ __forceinline__ float emit_p(const uint32_t (&sreg)[N], uint32_t tP, 
                                               __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
       pr[j] = ((j & 3) < EMU) ? exp2_pair_fma<(PT == kDtE4M3)>(x) : exp2_pair_sfu(x);
       if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
+    }
+    if constexpr (HALF_ARRIVE) {
+      if (c == N / 64) {   // the stores of the first half have had the time of this chunk's exponentials to land
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive_warp(bar_half);
+      }
     }
     if constexpr (PT == kDtE4M3) {   // 32 probabilities = 8 words = 8 columns
       uint32_t w[8];
@@ -217,13 +228,12 @@ __device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {
 // the row's raw scores (S_t, fp32 bits); on exit P has been written over S_t in tensor memory (tcgen05.st
 // issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first key tile of the row;
 // `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible column.
-// `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory (the UMMA
-// thread starts P V on those while the second half is still being computed); not used with the two-term P.
+// `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory; not used
+// with the two-term P.
 template <class CFG, int PT, int HD, int EMU>
 __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tO, float sl, bool first,
                                        bool mask_tile, int lim, bool split, uint32_t bar_half, float& m_ref,
                                        float& m_true, float& l) {
-  constexpr bool QUAD = (PT == kDtE4M3);
   // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
   // needs it at all depends only on the tile, so the test costs no vote.
   if (mask_tile) {   // lim: last visible local column of this row
@@ -231,20 +241,8 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
     for (int i = 0; i < 128; ++i)
       if (i > lim) sreg[i] = 0xff800000u;  // -inf
   }
-
-  // row maximum: sixteen independent chains of two-input max, then a tree
-  float mx[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) mx[i] = __uint_as_float(sreg[i]);
-#pragma unroll
-  for (int i = 16; i < 128; ++i) mx[i & 15] = fmaxf(mx[i & 15], __uint_as_float(sreg[i]));
-#pragma unroll
-  for (int w = 8; w >= 1; w >>= 1)
-#pragma unroll
-    for (int i = 0; i < w; ++i) mx[i] = fmaxf(mx[i], mx[i + w]);
-  const float rowmax = mx[0];
+  const float rowmax = row_max_n<128>(sreg);
   m_true = fmaxf(m_true, rowmax);
-
   if (first) {
     m_ref = (rowmax == -INFINITY) ? 0.f : rowmax;
   } else {
@@ -257,71 +255,16 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
         l *= alpha;
       }
       // O_t is complete up to tile j-1 here: the commit that released S_t(j) was issued after it.
-      uint32_t oreg[32];
-#pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        tmem_ld_x32(tO + c * 32, oreg);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-        tmem_st_x32(tO + c * 32, oreg);
-      }
-      tmem_wait_st();
+      rescale_o_row<HD>(tO, alpha);
     }
   }
   const float negm = CFG::PSHIFT - m_ref * sl;
-  const float2 sl2 = make_float2(sl, sl), negm2 = make_float2(negm, negm);
-  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-  auto gen_p = [&](auto split_c) {
-    constexpr bool SPLIT = decltype(split_c)::value;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    float2 pr[16];   // the 32 probabilities of this chunk, as pairs
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[32 * c + 2 * j]),
-                                              __uint_as_float(sreg[32 * c + 2 * j + 1])), sl2, negm2);
-      pr[j] = ((j & 3) < EMU) ? exp2_pair_fma<QUAD>(x) : exp2_pair_sfu(x);
-      if (j & 1) acc1 = __fadd2_rn(acc1, pr[j]); else acc0 = __fadd2_rn(acc0, pr[j]);
-    }
-    if constexpr (!SPLIT) {
-      if (c == 2) {   // the stores of chunks 0 and 1 have had the time of this chunk's exponentials to land
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive_warp(bar_half);
-      }
-    }
-    if constexpr (CFG::PESZ == 2) {
-      uint32_t hi[16];
-      [[maybe_unused]] uint32_t lo[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if constexpr (PT == kDtBF16) {
-          hi[j] = pack_bf16x2(pr[j].x, pr[j].y);
-          if constexpr (SPLIT)
-            lo[j] = pack_bf16x2(pr[j].x - __uint_as_float(hi[j] << 16), pr[j].y - __uint_as_float(hi[j] & 0xffff0000u));
-        } else {
-          hi[j] = pack_f16x2(pr[j].x, pr[j].y);
-        }
-      }
-      tmem_st_x16(tS + 16 * c, hi);
-      if constexpr (PT == kDtBF16) {
-        if constexpr (SPLIT) tmem_st_x16(tS + 64 + 16 * c, lo);
-      }
-    } else {
-      uint32_t w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) w[j] = pack_e4m3x4(pr[2 * j].x, pr[2 * j].y, pr[2 * j + 1].x, pr[2 * j + 1].y);
-      tmem_st_x8(tS + 8 * c, w);
-    }
-  }
-  };
   if constexpr (PT == kDtBF16) {
-    if (split) gen_p(std::true_type{}); else gen_p(std::false_type{});
+    if (split) l += emit_p<128, PT, EMU, true>(sreg, tS, tS + 64, sl, negm);
+    else l += emit_p<128, PT, EMU, false, true>(sreg, tS, 0u, sl, negm, bar_half);
   } else {
-    gen_p(std::false_type{});
+    l += emit_p<128, PT, EMU, false, true>(sreg, tS, 0u, sl, negm, bar_half);
   }
-  l += (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
 
 // O_t (fp32, tensor memory) * inv -> 16 bit -> shared-memory tile in the 128-byte swizzled layout the TMA

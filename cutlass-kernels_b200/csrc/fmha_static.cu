@@ -31,7 +31,8 @@ static std::mutex g_static_mu;
 static int* g_static_addr[64] = {nullptr};
 
 // Device address of the array on the current device; resolved once per device, with that device current.
-static int* static_scratch_for_current_device(int* err) {
+// (Not static: the bounded-wait self-test can be pointed at this array, see cfk_selftest_wait_gives_up_static.)
+int* static_scratch_for_current_device(int* err) {
   int dev = -1;
   if (note_cuda(cudaGetDevice(&dev), "cudaGetDevice") != cudaSuccess || dev < 0 || dev >= 64) {
     *err = CFK_ERR_NO_DRIVER;

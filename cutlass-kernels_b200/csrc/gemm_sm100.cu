@@ -92,8 +92,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
   const int bk = p.tf32 ? C::BK / 2 : C::BK;   // elements per 128-byte stage row
   const int nkb = (p.K + bk - 1) / bk;
 
-  // Both CTAs of a pair read the same word, so they skip or run together.
-  if (cta_should_skip(p.status)) return;
+  // One decision for the pair: both CTAs skip or both run (pair_should_skip).
+  if (pair_should_skip(p.status)) return;
   if (tid == 0) {
     for (int i = 0; i < C::NSTAGE; ++i) { mbar_init(bar_full + 8 * i, 2); mbar_init(bar_empty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 256); }

@@ -18,6 +18,9 @@ cudaError_t note_cuda(cudaError_t e, const char* what);
 // word the kernels write).  nullptr (and *err set) if there is no usable device.
 int* device_status_block(int* err);
 
+// Device address of the fixed scratch array that cfk_fmha_forward_static uses (fmha_static.cu); allocates nothing.
+int* static_scratch_for_current_device(int* err);
+
 inline int dtype_size(int dt) { return dt == CFK_E4M3 ? 1 : (dt == CFK_FP32 ? 4 : 2); }
 
 // Generic tiled descriptor.  dims/box are innermost first; strides_bytes has rank-1 entries.

@@ -288,11 +288,26 @@ __global__ void __launch_bounds__(32, 1) wait_gives_up_kernel(int* status, unsig
 }
 }  // namespace cfk
 
+static int launch_wait_gives_up(int* status, int limit_ms, cfk_stream_t stream) {
+  wait_gives_up_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)limit_ms * 1000000ull);
+  return note_cuda(cudaGetLastError(), "wait selftest launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+}
+
 extern "C" int cfk_selftest_wait_gives_up(int limit_ms, cfk_stream_t stream) {
   if (limit_ms < 1 || limit_ms > 1000) return CFK_ERR_INVALID_ARG;
   int err = CFK_OK;
   int* status = device_status_block(&err);
   if (!status) return err;
-  wait_gives_up_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)limit_ms * 1000000ull);
-  return note_cuda(cudaGetLastError(), "wait selftest launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
+  return launch_wait_gives_up(status, limit_ms, stream);
+}
+
+// The same wait, reporting into the status word of the fixed array that cfk_fmha_forward_static uses: the way to
+// see that entry point's own failure path (its status query, and the clearing of the word by the next call)
+// without a real failure.  Allocates nothing.
+extern "C" int cfk_selftest_wait_gives_up_static(int limit_ms, cfk_stream_t stream) {
+  if (limit_ms < 1 || limit_ms > 1000) return CFK_ERR_INVALID_ARG;
+  int err = CFK_OK;
+  int* status = cfk::static_scratch_for_current_device(&err);
+  if (!status) return err;
+  return launch_wait_gives_up(status, limit_ms, stream);
 }

@@ -40,13 +40,13 @@ static bool flag(int argc, char** argv, const char* name, std::string* value) {
 
 static void usage() {
   std::printf("cutlass_gemm\n\n  fp16 GEMM D = alpha * A * B + beta * C on sm_100a (tcgen05, CTA pairs).\n\nOptions:\n\n"
-              "  --help                      If specified, displays this usage statement\n\n"
-              "  --m=<int>                   Sets the M extent of the GEMM\n"
-              "  --n=<int>                   Sets the N extent of the GEMM\n"
-              "  --k=<int>                   Sets the K extent of the GEMM\n"
-              "  --alpha=<f32>               Epilogue scalar alpha\n"
-              "  --beta=<f32>                Epilogue scalar beta\n\n"
-              "  --iterations=<int>          Number of profiling iterations to perform.\n\n");
+              "  --help                      print this text and exit\n\n"
+              "  --m=<int>                   rows of A and of C, D (default 5120)\n"
+              "  --n=<int>                   columns of B and of C, D (default 4096)\n"
+              "  --k=<int>                   columns of A, rows of B: the reduction length (default 4096)\n"
+              "  --alpha=<f32>               factor of the product A * B (default 1)\n"
+              "  --beta=<f32>                factor of the source matrix C (default 0)\n\n"
+              "  --iterations=<int>          timed launches after the verified one (default 1000)\n\n");
 }
 
 static int download_f32(const void* dev, int dtype, size_t n, std::vector<float>* out) {

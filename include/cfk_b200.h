@@ -104,6 +104,10 @@ int cfk_fmha_forward(const cfk_fmha_args* args, cfk_stream_t stream);
  *   - A build whose kernels need more scratch than the array holds is refused with CFK_ERR_TOO_LARGE.
  *   - iterations == 0 launches nothing: it waits for `stream` and returns CFK_ERR_DEVICE_WAIT if the status
  *     word left by the preceding call is non-zero (cfk_device_status reads the allocated block only).
+ *   - Because every call clears the word on entry, a wait that gave up inside call N is forgotten by call
+ *     N + 1: a caller that wants to know puts an iterations == 0 query between the two (it synchronises
+ *     `stream`).  A launch that finds the word set does nothing, so without the query the outputs of call N
+ *     may be partly unwritten and nothing says so.
  */
 int cfk_fmha_forward_static(const cfk_fmha_args* args, cfk_stream_t stream);
 
@@ -196,6 +200,10 @@ int cfk_umma_peak(int dtype, int groups, double* flops_out, cfk_stream_t stream)
  * wait without a limit.
  */
 int cfk_selftest_wait_gives_up(int limit_ms, cfk_stream_t stream);
+/* The same wait, reporting into the fixed scratch array of cfk_fmha_forward_static instead of the allocated
+ * status block (and allocating nothing): makes that entry point's status query return CFK_ERR_DEVICE_WAIT once,
+ * so its failure path can be tested.  No counterpart in the reference. */
+int cfk_selftest_wait_gives_up_static(int limit_ms, cfk_stream_t stream);
 
 /*
  * Single-CTA UMMA self-test used by the GPU test-suite to prove each operand-descriptor form

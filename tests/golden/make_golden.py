@@ -32,6 +32,17 @@ def main():
         out.update({f"{tag}_q": q.astype(np.float16), f"{tag}_k": k.astype(np.float16), f"{tag}_v": v.astype(np.float16), f"{tag}_scale": np.float32(scale),
                     f"{tag}_causal": np.int32(causal), f"{tag}_o": r["o"].astype(np.float32),
                     f"{tag}_lse": r["lse"].astype(np.float32)})
+    # two more cases at a head dimension the CUDA kernels are built for, drawn from a generator of their own so that
+    # the arrays above keep their values
+    rng64 = np.random.default_rng(3081)
+    more = {"causal64": (1, 128, 128, 1, 64, True), "ragged64": (2, 77, 133, 2, 64, False)}
+    for tag, (B, Sq, Skv, H, D, causal) in more.items():
+        q, k, v = rounded(rng64, (B, Sq, H, D)), rounded(rng64, (B, Skv, H, D)), rounded(rng64, (B, Skv, H, D))
+        scale = 1.0 / math.sqrt(D)
+        r = attention_f64(q, k, v, scale, causal)
+        out.update({f"{tag}_q": q.astype(np.float16), f"{tag}_k": k.astype(np.float16), f"{tag}_v": v.astype(np.float16), f"{tag}_scale": np.float32(scale),
+                    f"{tag}_causal": np.int32(causal), f"{tag}_o": r["o"].astype(np.float32),
+                    f"{tag}_lse": r["lse"].astype(np.float32)})
     np.savez_compressed(os.path.join(HERE, "attention_small.npz"), **out)
     a = rng.uniform(-1, 1, (48, 80)).astype(np.float16).astype(np.float32)
     b = rng.uniform(-1, 1, (40, 80)).astype(np.float16).astype(np.float32)

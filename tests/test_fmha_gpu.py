@@ -347,15 +347,24 @@ FULL_SIZE = [
 @pytest.mark.parametrize("name,dtype,B,H,S,D,causal", FULL_SIZE)
 def test_fmha_full_size_properties(lib, oracle, cuda, name, dtype, B, H, S, D, causal):
     """At the sizes the benchmark runs: (1) with V = 1 every output is exactly the normalisation, i.e. 1;
-    (2) O is linear in V (V -> 2 V, a power of two, doubles O to the last bit of a normal fp16); (3) LSE matches the oracle on one
-    sampled (batch, head) slice and the output of that slice meets the tolerance; (4) two runs are bit-identical."""
+    (2) O is linear in V (V -> 2 V, a power of two, doubles O to the last bit of a normal fp16); (3) four (batch, head)
+    slices, the first and the last among them, match the oracle within the stated tolerance AND within the reference's
+    own acceptance rule (share of elements off by abs 5e-3 and rel 10 %: <= 0.0001 % for 16-bit inputs, 0.001 % for
+    e4m3, src/fmha-pipeline/fmha_forward.cu:638-639), LSE included; (4) two runs are bit-identical.  e4m3 inputs are
+    quantised with the per-tensor scale amax / 448, as the baseline configuration states."""
     n = B * S * H * D
     tdt = {0: torch.float16, 1: torch.bfloat16, 2: torch.uint8}[dtype]
     q, k, v = (torch.empty(B, S, H, D, dtype=tdt, device="cuda") for _ in range(3))
-    scale8 = 6.0 / 448.0
+    desc = [1.0] * 3
     for i, t in enumerate((q, k, v)):
-        lib.fill(t, dtype, n, 3081 + i, "normal", scale=(1.0 / scale8 if dtype == 2 else 1.0))
-    desc = [scale8] * 3 if dtype == 2 else [1.0] * 3
+        if dtype == 2:
+            f = torch.empty(n, dtype=torch.float32, device="cuda")
+            lib.fill(f, 3, n, 3081 + i, "normal")
+            desc[i] = float(f.abs().max()) / 448.0
+            lib.convert(f, 3, t, 2, n, 1.0 / desc[i])
+            del f
+        else:
+            lib.fill(t, dtype, n, 3081 + i, "normal")
     o = torch.empty(B, S, H, D, dtype=torch.float16, device="cuda")
     lse = torch.empty(B, H, S, dtype=torch.float32, device="cuda")
 
@@ -379,17 +388,18 @@ def test_fmha_full_size_properties(lib, oracle, cuda, name, dtype, B, H, S, D, c
     run(ones, 1.0, o1)
     tol1 = 1e-3 if dtype != 2 else 3e-2        # e4m3 P: the row sum is taken before P is rounded, the product after
     assert float((o1.float() - 1.0).abs().max()) <= tol1                   # (1)
-    # (3) one slice against the oracle
-    b, h = B - 1, H // 2
-    conv = lambda t, s: (lib_to_f32(lib, t[b:b + 1, :, h:h + 1, :].contiguous(), dtype) * s).cpu().numpy()
-    ref = oracle.attention(conv(q, desc[0]), conv(k, desc[1]), conv(v, desc[2]), 1.0 / math.sqrt(D), causal)
-    cmp = oracle.compare(o[b:b + 1, :, h:h + 1, :].float().cpu().numpy(), ref["o"])
-    assert cmp["nonfinite"] == 0
-    if dtype == 2:
-        assert cmp["rel_rms"] <= 3e-2, cmp
-    else:
-        assert cmp["max_abs"] <= 2e-3, cmp
-    assert np.abs(lse[b, h].cpu().numpy() - ref["lse"][0, 0]).max() <= (2e-2 if dtype == 2 else 2e-3)
+    # (3) four slices against the oracle
+    conv = lambda t, s, b, h: (lib_to_f32(lib, t[b:b + 1, :, h:h + 1, :].contiguous(), dtype) * s).cpu().numpy()
+    for (b, h) in sorted({(0, 0), (B - 1, H - 1), (B - 1, H // 2), (0, H // 3)}):
+        ref = oracle.attention(conv(q, desc[0], b, h), conv(k, desc[1], b, h), conv(v, desc[2], b, h),
+                               1.0 / math.sqrt(D), causal)
+        cmp = oracle.compare(o[b:b + 1, :, h:h + 1, :].float().cpu().numpy(), ref["o"])
+        assert cmp["nonfinite"] == 0, (b, h, cmp)
+        if dtype == 2:
+            assert cmp["rel_rms"] <= 3e-2 and cmp["mismatch_pct"] <= 0.001, (b, h, cmp)
+        else:
+            assert cmp["max_abs"] <= 2e-3 and cmp["mismatch_pct"] <= 0.0001, (b, h, cmp)
+        assert np.abs(lse[b, h].cpu().numpy() - ref["lse"][0, 0]).max() <= (2e-2 if dtype == 2 else 2e-3), (b, h)
 
 
 def lib_to_f32(lib, t, dtype):

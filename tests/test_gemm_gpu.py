@@ -45,10 +45,11 @@ def test_gemm_batched(lib, oracle, cuda):
     run(lib, oracle, 384, 512, 320, L=3)
 
 
-def test_gemm_linearity_at_full_size(lib, cuda):
+def test_gemm_linearity_at_full_size(lib, oracle, cuda):
     """8192^3 (the baseline's GEMM config): C(alpha=2) == 2 * C(alpha=1) in fp16 (power-of-two scaling
-    commutes with rounding while nothing overflows or is subnormal), and a sampled set of entries equals an
-    fp64 dot product of the same operands to fp16 rounding."""
+    commutes with rounding while nothing overflows or is subnormal); a sampled set of entries equals an
+    fp64 dot product of the same operands to fp16 rounding; and one full band of 256 rows and one full band of 256
+    columns of the result (each crossing every tile of the other direction) equal the oracle's."""
     n = 8192
     torch.manual_seed(1)
     a = (torch.rand(n, n, device="cuda") * 2 - 1).half()
@@ -64,6 +65,15 @@ def test_gemm_linearity_at_full_size(lib, cuda):
     for m, nn in idx.tolist():
         ref = float(a[m].double() @ b[nn].double())
         assert abs(float(c1[nn, m]) - ref) <= 2.0 ** -10 * max(1.0, abs(ref)) + 2e-3   # column-major C
+    af, bf = a.float().cpu().numpy(), b.float().cpu().numpy()
+    m0, n0 = 3 * 256 + 128, 29 * 256                     # the row band straddles two 256-row tiles
+    rows = oracle.gemm(af, bf, m_range=(m0, m0 + 256))[m0:m0 + 256]              # [256, N]
+    got_rows = c1[:, m0:m0 + 256].float().cpu().numpy().T                         # C is stored [N][M]
+    cols = oracle.gemm(bf[n0:n0 + 256], af)                                       # C^T band: [256, M]
+    got_cols = c1[n0:n0 + 256, :].float().cpu().numpy()
+    for got, ref in ((got_rows, rows), (got_cols, cols)):
+        tol = 2.0 ** -10 * np.maximum(np.abs(ref), 1.0) + 2e-3   # fp16 rounding of values up to ~150, fp32 summation order
+        assert (np.abs(got - ref) <= tol).all(), float(np.abs(got - ref).max())
 
 
 def test_gemm_separate_source_matrix_and_integer_operands(lib, oracle, cuda):

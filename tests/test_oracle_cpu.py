@@ -104,7 +104,7 @@ def test_fill_is_index_keyed(oracle):
 
 def test_golden_fixtures(oracle):
     data = np.load(os.path.join(GOLDEN, "attention_small.npz"))
-    for tag in ("c1", "causal", "ragged"):
+    for tag in ("c1", "causal", "ragged", "causal64", "ragged64"):
         q, k, v = data[f"{tag}_q"], data[f"{tag}_k"], data[f"{tag}_v"]
         causal = bool(data[f"{tag}_causal"])
         got = oracle.attention(q, k, v, float(data[f"{tag}_scale"]), causal)

@@ -50,3 +50,50 @@ def test_static_entry_point_rejects_what_the_other_rejects(lib, cuda):
     a = _args(lib, low, o, scales, 0, False)
     a.o = None
     assert lib.fmha_forward_static_raw(a) == 1
+
+
+def test_static_entry_point_allocates_no_device_memory(lib, cuda):
+    """The property the entry point is named for: after one warm-up call (which looks the array's address up), the
+    free device memory the driver reports does not move across further calls, whatever the shape."""
+    shapes = [(0, 2, 1024, 3, 128, True), (2, 1, 2048, 2, 128, False), (1, 1, 512, 2, 64, True), (0, 1, 640, 1, 256, False)]
+    prepared = []
+    for (dtype, B, S, H, D, causal) in shapes:
+        low, _, scales = make_qkv(dtype, B, S, S, H, D, seed=7 + S)
+        low = [x.cuda() for x in low]
+        o = torch.empty(B, S, H, D, device="cuda", dtype=torch.float16)
+        prepared.append((low, o, scales, dtype, causal))
+    assert lib.fmha_forward_static_raw(_args(lib, *prepared[0])) == 0       # warm-up: address lookup, module load
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for rep in range(3):
+        for pr in prepared:
+            assert lib.fmha_forward_static_raw(_args(lib, *pr)) == 0
+            assert lib.fmha_forward_static_raw(_args(lib, *pr, iterations=0)) == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
+def test_static_entry_point_reports_a_wait_that_gave_up_and_the_next_call_clears_it(lib, cuda):
+    """The entry point's own failure path, without a failure: the bounded-wait self-test (one warp, 50 ms, a barrier
+    nothing arrives on) reports into the fixed array.  The status query then says DEVICE_WAIT; the allocated status
+    block of the other entry point knows nothing of it; the next static call clears the word, computes correctly,
+    and the query is clean again."""
+    low, _, scales = make_qkv(0, 1, 512, 512, 2, 128, seed=3)
+    low = [x.cuda() for x in low]
+    want = torch.empty(1, 512, 2, 128, device="cuda", dtype=torch.float16)
+    assert lib.fmha_forward_raw(_args(lib, low, want, scales, 0, True)) == 0
+    lib.check_device()
+    got = torch.full_like(want, -2.0)
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True)) == 0
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True, iterations=0)) == 0
+    assert lib.selftest_wait_gives_up_static(0) == 1                        # limits outside 1..1000 ms are refused
+    assert lib.selftest_wait_gives_up_static(50) == 0
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True, iterations=0)) == 6    # CFK_ERR_DEVICE_WAIT
+    assert lib.device_status() == (0, 0)                                    # the allocated block is a different word
+    # the query does not clear the word; the next call does, on its stream, before its launches
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True, iterations=0)) == 6
+    got.fill_(-2.0)
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True)) == 0
+    assert lib.fmha_forward_static_raw(_args(lib, low, got, scales, 0, True, iterations=0)) == 0
+    assert torch.equal(got, want)
