@@ -10,8 +10,10 @@
 //              fetches only what its own SM consumes)
 //   warp 1     UMMA issuer (leader CTA only): 256 x 256 x 16 tcgen05.mma over the pair, two accumulator
 //              buffers of 256 TMEM columns per CTA
-//   warps 2-5  epilogue: TMEM -> registers -> alpha/beta -> 16-bit -> global, overlapped with the next
-//              tile's main loop
+//   warps 2-5  epilogue: TMEM -> registers -> alpha/beta -> output type -> a swizzled staging tile in shared
+//              memory (128 rows x 128 bytes, two of them) -> TMA store, overlapped with the next tile's main
+//              loop.  (The reference writes its register accumulators to global memory thread by thread,
+//              gemm.cu:329-331.)
 //
 // The pair halves the B-operand bytes each SM reads from shared memory per FLOP, which is what bounds a
 // single-CTA 128 x 256 tile.  Pairs are persistent (one per two SMs) and walk the tile list in bands of
@@ -28,7 +30,8 @@
 
 namespace cfk {
 
-constexpr int kErrGemmFull = 201, kErrGemmEmpty = 202, kErrGemmAccFull = 203, kErrGemmAccEmpty = 204;
+constexpr int kErrGemmFull = 201, kErrGemmEmpty = 202, kErrGemmAccFull = 203, kErrGemmAccEmpty = 204,
+              kErrGemmStaged = 205, kErrGemmStageFree = 206;
 
 struct GemmParams {
   int R, Cn, K, L;       // rows of X / D, rows of Y (= columns of D), reduction length, batch count
@@ -48,7 +51,8 @@ struct GemmCfg {
   static constexpr int TILE = 256;                            // tile edge of the CTA pair
   static constexpr int XB = BM * BK * 2, YB = BNH * BK * 2;   // bytes per stage
   static constexpr int NSTAGE = 6;
-  static constexpr int SMEM_BYTES = 1024 + NSTAGE * (XB + YB) + 256;
+  static constexpr int STAGEB = 128 * 128;                    // output staging tile: 128 rows x 128 bytes
+  static constexpr int SMEM_BYTES = 1024 + NSTAGE * (XB + YB) + 2 * STAGEB + 256;
   static constexpr int NTHREADS = 192;
   static constexpr int BAND = 8;
 };
@@ -67,20 +71,24 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, 
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
+            const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
   using C = GemmCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sX = smem_base;
   const uint32_t sY = smem_base + C::NSTAGE * C::XB;
-  const uint32_t sBar = sY + C::NSTAGE * C::YB;
+  const uint32_t sStage = sY + C::NSTAGE * C::YB;             // [2] output staging tiles
+  const uint32_t sBar = sStage + 2 * C::STAGEB;
   const uint32_t bar_full = sBar;                            // [NSTAGE] leader: both CTAs' loads of a stage landed
   const uint32_t bar_empty = sBar + 8 * C::NSTAGE;           // [NSTAGE] each CTA: its stage was consumed
   const uint32_t bar_acc_full = bar_empty + 8 * C::NSTAGE;   // [2] each CTA: accumulator complete
   const uint32_t bar_acc_empty = bar_acc_full + 16;          // [2] leader: both epilogues have read it
+  const uint32_t bar_staged = bar_acc_empty + 16;            // [2] a staging tile is complete (4 epilogue warps)
+  const uint32_t bar_stage_free = bar_staged + 16;           // [2] the TMA store has read a staging tile
   uint8_t* gBar = smem_gen + (sBar - smem_base);
-  const uint32_t off_misc = 8 * (2 * C::NSTAGE + 4);
+  const uint32_t off_misc = 8 * (2 * C::NSTAGE + 8);
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gBar + off_misc + 4);
   const AbortCtx actx{s_abort, p.status};
@@ -97,6 +105,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
   if (tid == 0) {
     for (int i = 0; i < C::NSTAGE; ++i) { mbar_init(bar_full + 8 * i, 2); mbar_init(bar_empty + 8 * i, 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(bar_acc_full + 8 * i, 1); mbar_init(bar_acc_empty + 8 * i, 256); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_staged + 8 * i, 4); mbar_init(bar_stage_free + 8 * i, 1); }
     *s_abort = 0u;
     fence_barrier_init();
   }
@@ -104,7 +113,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(s_tmem_base)), 512);
     tmem_relinquish_pair();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_y); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tm_x); tma_prefetch_desc(&tm_y); tma_prefetch_desc(&tm_d); }
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();           // the peer's barriers exist before anything is signalled on them
@@ -172,12 +181,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
       }
     }
   } else {
-    // epilogue warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31
+    // epilogue warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31.  A tile leaves in chunks of 128 bytes per
+    // row (64 columns, 32 for fp32 output): every thread turns its row's part of the accumulator into the output
+    // type and writes it into a staging tile in the 128-byte swizzled layout; when the four warps have done so, one
+    // thread hands the tile to a TMA store, which clips it at the edges of D.  Two staging tiles alternate.
     const int q = warp & 3;
+    const int r = q * 32 + lane;                       // row within this CTA's 128 rows
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    const int row_in_tile = (int)rank * C::BM + q * 32 + lane;
+    const int row_in_tile = (int)rank * C::BM + r;
     const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
+    const int esz = p.tf32 ? 4 : 2;
+    const int ccols = 128 / esz;                       // columns per chunk
+    const int nchunk = C::TILE / ccols;
+    const bool storer = (warp == 2 && lane == 0);
     int local = 0;
+    uint32_t n = 0;                                    // chunks staged so far: chunk n uses staging tile n & 1
     bool ok = true;
     for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
       int tr, tc, b;
@@ -188,73 +206,107 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
       tc_fence_after_sync();
       const int row = tr * C::TILE + row_in_tile;
       const int col0 = tc * C::TILE;
-      uint16_t* drow = reinterpret_cast<uint16_t*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
-      const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.src) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+      const size_t src_row = (size_t)b * p.d_batch + (size_t)row * p.ldd;
 #pragma unroll 1
-      for (int c = 0; c < C::TILE / 32; ++c) {
-        uint32_t acc[32];
-        tmem_ld_x32(tmem_base + lane_base + buf * 256 + c * 32, acc);
-        tmem_wait_ld();
-        if (row < p.R && p.tf32) {
-          float* drow32 = reinterpret_cast<float*>(p.d) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
-          const float* srow32 = reinterpret_cast<const float*>(p.src) + (size_t)b * p.d_batch + (size_t)row * p.ldd + col0;
+      for (int ch = 0; ch < nchunk; ++ch, ++n) {
+        const uint32_t sb = n & 1u;
+        const uint32_t stage = sStage + sb * C::STAGEB;
+        if (n >= 2u) {   // the store that last used this staging tile has read it
+          ok = mbar_wait_warp(bar_stage_free + 8 * sb, ((n >> 1) & 1u) ^ 1u, actx, kErrGemmStageFree);
+          if (!ok) break;
+        }
+        const uint32_t row_addr = stage + r * 128;
+#pragma unroll 1
+        for (int h = 0; h < ccols / 32; ++h) {         // 32 accumulator columns at a time
+          uint32_t acc[32];
+          const int cbase = ch * ccols + h * 32;       // first of these columns within the tile
+          tmem_ld_x32(tmem_base + lane_base + buf * 256 + cbase, acc);
+          tmem_wait_ld();
+          float v[32];
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {   // 4 columns = 16 bytes per group
-            const int col = col0 + c * 32 + g * 4;
-            if (col < p.Cn) {
-              float4 v;
-              v.x = p.alpha * __uint_as_float(acc[g * 4]);     v.y = p.alpha * __uint_as_float(acc[g * 4 + 1]);
-              v.z = p.alpha * __uint_as_float(acc[g * 4 + 2]); v.w = p.alpha * __uint_as_float(acc[g * 4 + 3]);
-              if (p.beta != 0.f) {
-                const float4 old = *reinterpret_cast<const float4*>(srow32 + c * 32 + g * 4);
-                v.x += p.beta * old.x; v.y += p.beta * old.y; v.z += p.beta * old.z; v.w += p.beta * old.w;
-              }
-              *reinterpret_cast<float4*>(drow32 + c * 32 + g * 4) = v;
-            }
-          }
-        } else if (row < p.R) {
+          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(acc[i]);
+          if (p.beta != 0.f && row < p.R) {            // the source matrix: this thread's row, straight from global memory
+            if (p.tf32) {
+              const float* srow = reinterpret_cast<const float*>(p.src) + src_row + col0 + cbase;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {   // 8 columns = 16 bytes per group
-            const int col = col0 + c * 32 + g * 8;
-            if (col < p.Cn) {
-              float v[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] = p.alpha * __uint_as_float(acc[g * 8 + i]);
-              uint4* dst = reinterpret_cast<uint4*>(drow + c * 32 + g * 8);
-              if (p.beta != 0.f) {
-                const uint4 old = *reinterpret_cast<const uint4*>(srow + c * 32 + g * 8);
-                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  float lo, hi;
-                  if (p.bf16) {
-                    lo = __uint_as_float(ow[i] << 16);
-                    hi = __uint_as_float(ow[i] & 0xffff0000u);
-                  } else {
-                    const __half2 h = *reinterpret_cast<const __half2*>(&ow[i]);
-                    lo = __low2float(h);
-                    hi = __high2float(h);
-                  }
-                  v[2 * i] += p.beta * lo;
-                  v[2 * i + 1] += p.beta * hi;
+              for (int g = 0; g < 8; ++g) {
+                if (col0 + cbase + g * 4 < p.Cn) {
+                  const float4 old = *reinterpret_cast<const float4*>(srow + g * 4);
+                  v[g * 4] += p.beta * old.x; v[g * 4 + 1] += p.beta * old.y;
+                  v[g * 4 + 2] += p.beta * old.z; v[g * 4 + 3] += p.beta * old.w;
                 }
               }
-              uint4 out;
-              if (p.bf16) {
-                out.x = pack_bf16x2(v[0], v[1]); out.y = pack_bf16x2(v[2], v[3]);
-                out.z = pack_bf16x2(v[4], v[5]); out.w = pack_bf16x2(v[6], v[7]);
-              } else {
-                out.x = pack_f16x2(v[0], v[1]); out.y = pack_f16x2(v[2], v[3]);
-                out.z = pack_f16x2(v[4], v[5]); out.w = pack_f16x2(v[6], v[7]);
+            } else {
+              const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.src) + src_row + col0 + cbase;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + cbase + g * 8 < p.Cn) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(srow + g * 8);
+                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    float lo, hi;
+                    if (p.bf16) {
+                      lo = __uint_as_float(ow[i] << 16);
+                      hi = __uint_as_float(ow[i] & 0xffff0000u);
+                    } else {
+                      const __half2 hh = *reinterpret_cast<const __half2*>(&ow[i]);
+                      lo = __low2float(hh);
+                      hi = __high2float(hh);
+                    }
+                    v[g * 8 + 2 * i] += p.beta * lo;
+                    v[g * 8 + 2 * i + 1] += p.beta * hi;
+                  }
+                }
               }
-              *dst = out;
+            }
+          }
+          // 16-byte pieces of the row, piece index XOR (row & 7): the 128-byte swizzle the TMA store undoes
+          if (p.tf32) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const uint32_t piece = (uint32_t)g ^ (uint32_t)(r & 7);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + piece * 16),
+                           "r"(__float_as_uint(v[g * 4])), "r"(__float_as_uint(v[g * 4 + 1])),
+                           "r"(__float_as_uint(v[g * 4 + 2])), "r"(__float_as_uint(v[g * 4 + 3])) : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint32_t w0, w1, w2, w3;
+              if (p.bf16) {
+                w0 = pack_bf16x2(v[g * 8], v[g * 8 + 1]); w1 = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+                w2 = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]); w3 = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+              } else {
+                w0 = pack_f16x2(v[g * 8], v[g * 8 + 1]); w1 = pack_f16x2(v[g * 8 + 2], v[g * 8 + 3]);
+                w2 = pack_f16x2(v[g * 8 + 4], v[g * 8 + 5]); w3 = pack_f16x2(v[g * 8 + 6], v[g * 8 + 7]);
+              }
+              const uint32_t piece = (uint32_t)(h * 4 + g) ^ (uint32_t)(r & 7);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + piece * 16), "r"(w0), "r"(w1),
+                           "r"(w2), "r"(w3) : "memory");
             }
           }
         }
+        if (ch == nchunk - 1) {   // the accumulator has been read: the next tile but one may overwrite it
+          tc_fence_before_sync();
+          mbar_arrive_cluster(leader_acc_empty + 8 * buf);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive_warp(bar_staged + 8 * sb);
+        if (storer) {
+          if (!mbar_wait(bar_staged + 8 * sb, (n >> 1) & 1u, actx, kErrGemmStaged)) { ok = false; }
+          else {
+            tma_store_3d(&tm_d, stage, col0 + ch * ccols, tr * C::TILE + (int)rank * C::BM, b);
+            tma_store_commit();
+            tma_store_wait_read1();            // every store but this one has read its staging tile
+            if (n >= 1u) mbar_arrive(bar_stage_free + 8 * (sb ^ 1u));
+          }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
       }
-      tc_fence_before_sync();
-      mbar_arrive_cluster(leader_acc_empty + 8 * buf);
     }
+    if (storer) tma_store_wait_read0();
   }
 
   tc_fence_before_sync();
@@ -301,6 +353,13 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   if ((rc = encode_tiled(&tm_x, a->dtype, 3, x, xd, xs, xb, 128))) return rc;
   if ((rc = encode_tiled(&tm_y, a->dtype, 3, y, yd, ys, yb, 128))) return rc;
 
+  // D (row-major R x Cn per batch) for the TMA store of the epilogue: boxes of 128 rows x 128 bytes
+  CUtensorMap tm_d;
+  const uint64_t dd[3] = {(uint64_t)Cn, (uint64_t)R, (uint64_t)a->l};
+  const uint64_t ds[2] = {(uint64_t)Cn * esz, (uint64_t)Cn * esz * (uint64_t)R};
+  const uint32_t db[3] = {bk, GemmCfg::BM, 1};
+  if ((rc = encode_tiled(&tm_d, a->dtype, 3, a->c, dd, ds, db, 128))) return rc;
+
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   p.R = R; p.Cn = Cn; p.K = a->k; p.L = a->l;
@@ -332,6 +391,6 @@ extern "C" int cfk_gemm(const cfk_gemm_args* a, cfk_stream_t stream) {
   const long long pairs = total < sm_count / 2 ? total : sm_count / 2;   // one CTA pair per two SMs
   const int grid = (int)(2 * pairs);
   for (int it = 0; it < a->iterations; ++it)
-    gemm_kernel<<<grid, GemmCfg::NTHREADS, GemmCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tm_x, tm_y, p);
+    gemm_kernel<<<grid, GemmCfg::NTHREADS, GemmCfg::SMEM_BYTES, (cudaStream_t)stream>>>(tm_x, tm_y, tm_d, p);
   return note_cuda(cudaGetLastError(), "gemm launch") == cudaSuccess ? CFK_OK : CFK_ERR_LAUNCH;
 }
