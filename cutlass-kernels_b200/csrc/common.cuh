@@ -106,6 +106,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
   return __all_sync(0xffffffffu, ok);
 }
 
+// Tear-down of a CTA whose roles gave up: what it has in flight (TMA copies into its shared memory, UMMAs into its
+// tensor memory) signals barriers that nobody waits on any more, so every thread lets a fixed time pass, far longer
+// than such an operation takes and bounded, before shared and tensor memory are given back.
+__device__ __forceinline__ void settle_if_aborted(volatile uint32_t* cta_abort) {
+  if (*cta_abort) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+}
+
 // CTA-uniform test of the status word (one thread reads, everybody gets the same answer).
 __device__ __forceinline__ bool cta_should_skip(const int* status) {
   __shared__ int s_skip;

@@ -351,6 +351,7 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
 
   // ---- tear-down ----
+  settle_if_aborted(s_abort);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 4) {

@@ -478,6 +478,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }
 
   // ---- tear-down: no CTA leaves while its peer may still read its shared memory or signal its barriers
+  settle_if_aborted(s_abort);
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();

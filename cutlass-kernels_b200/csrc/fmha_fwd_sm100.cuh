@@ -350,6 +350,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 
   // ---- tear-down ----
+  settle_if_aborted(s_abort);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 8) {

@@ -8,8 +8,7 @@ constexpr int kDtF16 = 0, kDtBF16 = 1, kDtE4M3 = 2;
 // Where a bounded wait gave up (stored in the status word).
 constexpr int kErrFmhaQFull = 101, kErrFmhaKvFull = 102, kErrFmhaKvEmpty = 103, kErrFmhaSFull = 104,
               kErrFmhaPFull = 105, kErrFmhaOFull = 106, kErrFmhaOStaged = 107, kErrFmhaRowMax = 112,
-              kErrFmhaCorrReq = 113, kErrFmhaCorrDone = 114, kErrFmhaOFree = 115, kErrFmhaQFree = 116,
-              kErrFmhaStats = 117, kErrFmhaCorrPv = 118;
+              kErrFmhaOFree = 115, kErrFmhaStats = 117, kErrFmhaCorrPv = 118;
 
 struct FmhaParams {
   int B, H, Sq, Skv;

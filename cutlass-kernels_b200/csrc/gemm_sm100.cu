@@ -309,6 +309,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
     if (storer) tma_store_wait_read0();
   }
 
+  settle_if_aborted(s_abort);
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();           // no CTA leaves while its peer may still read its shared memory or signal it
