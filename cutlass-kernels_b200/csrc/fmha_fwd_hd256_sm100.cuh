@@ -22,7 +22,6 @@
 
 namespace cfk {
 
-constexpr int kErrFmhaPvDone256 = 111;
 
 template <int DT>
 struct FmhaHd256Cfg {

@@ -28,7 +28,6 @@
 
 namespace cfk {
 
-constexpr int kErrFmhaSFree = 108, kErrFmhaPvDone = 109, kErrFmhaMaxPub = 110;
 
 template <int DT>
 struct FmhaPairCfg {

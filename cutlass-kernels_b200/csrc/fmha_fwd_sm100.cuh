@@ -53,7 +53,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_p_full = bar_s_full + 16;               // [2][2]: per tile, P of keys 0-63 / of keys 64-127
   const uint32_t bar_o_full = bar_p_full + 32;               // [2]
   const uint32_t bar_o_staged = bar_o_full + 16;             // [2]
-  const uint32_t off_misc = (bar_o_staged + 16) - sBar;
+  const uint32_t bar_s_read = bar_o_staged + 16;             // [2] SEP_P: S_t is in the softmax registers (4 warps)
+  const uint32_t bar_pv_done = bar_s_read + 16;              // [2] SEP_P: O_t += P_t V_j is complete
+  const uint32_t off_misc = (bar_pv_done + 16) - sBar;
+  static_assert(8 + 16 * C::NSLOT + 16 + 32 + 16 + 16 + 16 + 16 + 16 <= C::BARB, "barrier block overflows");
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gBar + off_misc + 4);
   const AbortCtx actx{s_abort, p.status};
@@ -112,6 +115,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_p_full + 16 * t + 8, 4);
       mbar_init(bar_o_full + 8 * t, 1);
       mbar_init(bar_o_staged + 8 * t, 128);
+      mbar_init(bar_s_read + 8 * t, 4);
+      mbar_init(bar_pv_done + 8 * t, 1);
     }
     *s_abort = 0u;
     fence_barrier_init();
@@ -138,6 +143,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (p.causal) { const int v0 = qblk * 256 + diag_off + 1; visible = v0 < visible ? v0 : visible; }
     split = visible < p.split_keys;
   }
+  // How far Q K^T runs ahead of P V for one query tile.  With P over S (1) the scores of key tile j+1 are computed
+  // after P_j V_j has consumed P.  With buffers of its own for P (2) Q K_{j+1}^T is issued as soon as the softmax
+  // warps hold S_j in registers, so S_{j+1} is there long before they have finished tile j.  The two-term P keeps
+  // its second term in the upper half of S and therefore the first order.
+  const int ahead = (C::SEP_P && !split) ? 2 : 1;
 
   if (warp >= 8) {
    // Third warpgroup: hands most of its registers to the softmax warpgroups.
@@ -149,17 +159,21 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive_expect_tx(bar_q_full, q_bytes);
       for (int t = 0; t < 2; ++t)
         if (n_of(t) > 0) tma_load_5d(sQ + t * C::TILEB, &tm_q, bar_q_full, 0, qblk * 256 + t * 128, 0, head, batch);
+      // Tiles enter the ring in the order the UMMA warp consumes them: K_0 (.. K_{ahead-1}), then V_j, K_{j+ahead}.
       int idx = 0;
       bool ok = true;
+      auto load_tile = [&](bool is_v, int j) {
+        const int slot = idx % C::NSLOT;
+        const uint32_t ph = (idx / C::NSLOT) & 1;
+        ++idx;
+        if (!mbar_wait(bar_kv_empty + 8 * slot, ph ^ 1u, actx, kErrFmhaKvEmpty)) { ok = false; return; }
+        mbar_arrive_expect_tx(bar_kv_full + 8 * slot, is_v ? C::VTILEB : C::TILEB);
+        tma_load_5d(sRing + slot * C::SLOTB, is_v ? &tm_v : &tm_k, bar_kv_full + 8 * slot, 0, j * C::BN, 0, head, batch);
+      };
+      for (int j = 0; j < ahead && j < n_kv && ok; ++j) load_tile(false, j);
       for (int j = 0; j < n_kv && ok; ++j) {
-        for (int which = 0; which < 2; ++which, ++idx) {
-          const int slot = idx % C::NSLOT;
-          const uint32_t ph = (idx / C::NSLOT) & 1;
-          if (!mbar_wait(bar_kv_empty + 8 * slot, ph ^ 1u, actx, kErrFmhaKvEmpty)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_kv_full + 8 * slot, which == 0 ? C::TILEB : C::VTILEB);
-          tma_load_5d(sRing + slot * C::SLOTB, which == 0 ? &tm_k : &tm_v, bar_kv_full + 8 * slot, 0, j * C::BN, 0,
-                      head, batch);
-        }
+        load_tile(true, j);
+        if (j + ahead < n_kv && ok) load_tile(false, j + ahead);
       }
     }
    } else if (warp == 8) {
@@ -189,7 +203,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_pv_half = [&](int t, int slot, int half, uint32_t accumulate) {
         const uint64_t b0 = desc_advance_lo(bv0, slot * C::SLOTB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
-        const uint32_t a = tmem_base + t * 128;
+        const uint32_t a = tmem_base + (C::SEP_P ? C::P_COL0 + t * 64 : t * 128);
 #pragma unroll
         for (int k2 = 0; k2 < C::PV_KSTEPS / 2; ++k2) {
           const int kk = half * (C::PV_KSTEPS / 2) + k2;
@@ -208,24 +222,44 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       };
 
+      // The ring is consumed in the producer's order: K_0 (.. K_{ahead-1}), then V_j, K_{j+ahead}.
+      int idx = 0;
+      auto next_slot = [&](int& slot, uint32_t& ph) {
+        slot = idx % C::NSLOT;
+        ph = (uint32_t)(idx / C::NSLOT) & 1u;
+        ++idx;
+      };
       CFK_PROF_DECL(4)
       ok = mbar_wait_warp(bar_q_full, 0, actx, kErrFmhaQFull);
-      if (ok) ok = mbar_wait_warp(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
-      CFK_PROF_MARK(0)
-      if (ok) {
+      // Q K_j^T for j < ahead: the first needs nothing but its operands, the second (SEP_P) that S_0 has been read
+      for (int j = 0; j < ahead && j < n_kv && ok; ++j) {
+        int kslot;
+        uint32_t kph;
+        next_slot(kslot, kph);
+        ok = mbar_wait_warp(bar_kv_full + 8 * kslot, kph, actx, kErrFmhaKvFull);
+        CFK_PROF_MARK(0)
+        if (!ok) break;
         tc_fence_after_sync();
-        for (int t = 0; t < 2; ++t)
-          if (n_of(t) > 0) {
-            issue_qk(t, 0);
-            umma_commit_e<false>(bar_s_full + 8 * t, leader);
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= n_of(t)) continue;
+          if (j > 0) {
+            ok = mbar_wait_warp(bar_s_read + 8 * t, (uint32_t)(j - 1) & 1u, actx, kErrFmhaSRead);
+            if (!ok) break;
+            tc_fence_after_sync();
           }
-        umma_commit_e<false>(bar_kv_empty + 0, leader);
+          issue_qk(t, kslot);
+          umma_commit_e<false>(bar_s_full + 8 * t, leader);
+        }
+        if (ok) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
       }
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int vidx = 2 * j + 1, kidx = 2 * j + 2;
-        const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
+        int vslot, kslot = 0;
+        uint32_t vph, kph = 0;
+        next_slot(vslot, vph);
+        const bool have_k = j + ahead < n_kv;
+        if (have_k) next_slot(kslot, kph);
         CFK_PROF_MARK(3)
-        ok = mbar_wait_warp(bar_kv_full + 8 * vslot, (vidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+        ok = mbar_wait_warp(bar_kv_full + 8 * vslot, vph, actx, kErrFmhaKvFull);
         CFK_PROF_MARK(1)
         bool k_ready = false;
         for (int t = 0; t < 2 && ok; ++t) {
@@ -249,22 +283,26 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           } else {
             issue_pv_half(t, vslot, 1, 1u);
           }
-          if (j + 1 < n_of(t)) {
-            if (!k_ready) {
-              ok = mbar_wait_warp(bar_kv_full + 8 * kslot, (kidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+          if constexpr (C::SEP_P) umma_commit_e<false>(bar_pv_done + 8 * t, leader);
+          if (j == n_of(t) - 1) umma_commit_e<false>(bar_o_full + 8 * t, leader);
+          if (j + ahead < n_of(t)) {
+            if (ahead == 2) {   // the softmax warps hold S_t(j+1) in registers: its buffer may take S_t(j+2)
+              ok = mbar_wait_warp(bar_s_read + 8 * t, (uint32_t)(j + 1) & 1u, actx, kErrFmhaSRead);
               if (!ok) break;
-              tc_fence_after_sync();
+            }
+            if (!k_ready) {
+              ok = mbar_wait_warp(bar_kv_full + 8 * kslot, kph, actx, kErrFmhaKvFull);
+              if (!ok) break;
               k_ready = true;
             }
+            tc_fence_after_sync();
             issue_qk(t, kslot);
             umma_commit_e<false>(bar_s_full + 8 * t, leader);
-          } else {
-            umma_commit_e<false>(bar_o_full + 8 * t, leader);
           }
         }
         if (ok) {
           umma_commit_e<false>(bar_kv_empty + 8 * vslot, leader);
-          if (j + 1 < n_kv) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
+          if (have_k) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
         }
       }
       CFK_PROF_MARK(3)
@@ -278,6 +316,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r = tid & 127;               // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + t * 128;
+    const uint32_t tP = C::SEP_P ? tmem_base + lane_base + C::P_COL0 + t * 64 : tS;
     const uint32_t tO = tmem_base + lane_base + C::O_COL0 + t * HD;
     const int row_g = qblk * 256 + t * 128 + r;     // global query row
     const int n_my = n_of(t);
@@ -290,11 +329,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     float l = 0.f;
     bool ok = true;
     uint32_t sreg[128];
+    [[maybe_unused]] uint32_t s_seen = 0u;
 
     CFK_PROF_DECL(8)
     for (int j = 0; j < n_my; ++j) {
       CFK_PROF_MARK(7)
-      ok = mbar_wait_warp(bar_s_full + 8 * t, j & 1, actx, kErrFmhaSFull);
+      if (!(C::SEP_P && __all_sync(0xffffffffu, s_seen)))   // SEP_P: looked at while the previous tile's P was on its way
+        ok = mbar_wait_warp(bar_s_full + 8 * t, j & 1, actx, kErrFmhaSFull);
       CFK_PROF_MARK(0)
       if (!ok) break;
       tc_fence_after_sync();
@@ -302,7 +343,18 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_x32(tS + 32, sreg + 32);
       tmem_ld_x32(tS + 64, sreg + 64);
       tmem_ld_x32(tS + 96, sreg + 96);
+      // SEP_P: an early look at "P V of the previous key tile is complete", used after the row maximum (measured:
+      // looking here, behind the loads, beats looking before them or only when the answer is needed, 824 against
+      // 787 TFLOP/s at d = 64 fp16)
+      uint32_t pv_seen = (j > 0 && C::SEP_P) ? 0u : 1u;
+      if constexpr (C::SEP_P) {
+        if (j > 0) pv_seen = mbar_test_wait(bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u);
+      }
       tmem_wait_ld();
+      if constexpr (C::SEP_P) {   // S_t may take the scores of the next key tile
+        tc_fence_before_sync();
+        mbar_arrive_warp(bar_s_read + 8 * t);
+      }
       CFK_PROF_MARK(1)
 
       if constexpr (DUMP) dump_scores(p, sreg, batch, head, row_g, j * C::BN);
@@ -310,10 +362,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       {
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }
-        softmax_step<C, PT, HD, EMU>(sreg, tS, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim, lim - j * C::BN, split,
-                                     bar_p_full + 16 * t, m_ref, m_true, l);
+        ok = softmax_step<C, PT, HD, EMU>(sreg, tS, tP, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim, lim - j * C::BN,
+                                          split, bar_p_full + 16 * t, bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u, pv_seen,
+                                          actx, m_ref, m_true, l);
+        if (!ok) break;
       }
       CFK_PROF_MARK(3)
+      // SEP_P: the scores of the next key tile are as a rule complete by now; the look overlaps the wait for the stores
+      if constexpr (C::SEP_P) s_seen = mbar_test_wait(bar_s_full + 8 * t, (uint32_t)(j + 1) & 1u);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar_p_full + 16 * t + 8);

@@ -55,6 +55,10 @@ struct FmhaCfg {
   static constexpr int PCOLS = BN * PESZ / 4;      // TMEM columns taken by P
   static constexpr int TMEM_COLS = 512;
   static constexpr int O_COL0 = 256;
+  // Head dimension 64 leaves 128 columns of tensor memory free (2 x S + 2 x O = 384): P gets buffers of its own
+  // there instead of being written over S, so the next Q K^T of a tile does not have to wait for its P V.
+  static constexpr bool SEP_P = (HD == 64);
+  static constexpr int P_COL0 = 384;               // P_t at P_COL0 + 64 t (SEP_P only)
   static constexpr uint32_t FMT_IN = (DT == kDtBF16) ? kFmtBF16 : 0u;   // f16 / e4m3 are both code 0
   static constexpr uint32_t FMT_P = (PT == kDtBF16) ? kFmtBF16 : 0u;
   static constexpr uint32_t IDESC_QK = make_idesc(1, FMT_IN, FMT_IN, 0, 0, BM, BN);
@@ -238,15 +242,21 @@ __device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {
 }
 
 // One key tile of the online softmax for the thread that owns a query row.  On entry sreg[0..127] holds
-// the row's raw scores (S_t, fp32 bits); on exit P has been written over S_t in tensor memory (tcgen05.st
-// issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first key tile of the row;
-// `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible column.
-// `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory; not used
-// with the two-term P.
+// the row's raw scores (S_t, fp32 bits); on exit P has been written to tensor memory at tP (over S_t, or a buffer
+// of its own with SEP_P; tcgen05.st issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first
+// key tile of the row; `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible
+// column.  `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory; not
+// used with the two-term P, whose second term goes to the upper half of S_t.
+// With SEP_P the S buffer no longer says that P V of the previous key tile has run (the next Q K^T was issued
+// before it), so the thread waits for `bar_pv_done` before it touches O_t or the P buffer again.  Returns false if
+// that wait gave up.  A look at a barrier costs one to several hundred clocks even when the barrier is complete
+// (the tensor core's operand reads keep the shared-memory port busy), so the caller looks early, with a test that
+// cannot put the warp to sleep, and hands the answer in.
 template <class CFG, int PT, int HD, int EMU>
-__device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tO, float sl, bool first,
-                                       bool mask_tile, int lim, bool split, uint32_t bar_half, float& m_ref,
-                                       float& m_true, float& l) {
+__device__ __forceinline__ bool softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tP, uint32_t tO, float sl,
+                                             bool first, bool mask_tile, int lim, bool split, uint32_t bar_half,
+                                             uint32_t bar_pv_done, uint32_t pv_parity, uint32_t pv_seen,
+                                             const AbortCtx& actx, float& m_ref, float& m_true, float& l) {
   // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
   // needs it at all depends only on the tile, so the test costs no vote.
   if (mask_tile) {   // lim: last visible local column of this row
@@ -256,6 +266,12 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
   }
   const float rowmax = row_max_n<128>(sreg);
   m_true = fmaxf(m_true, rowmax);
+  if constexpr (CFG::SEP_P) {
+    if (!first) {   // `pv_seen`: an early look (issued before the row maximum) already found it complete
+      if (!__all_sync(0xffffffffu, pv_seen) && !mbar_wait_warp(bar_pv_done, pv_parity, actx, kErrFmhaPvDone)) return false;
+      tc_fence_after_sync();
+    }
+  }
   if (first) {
     m_ref = (rowmax == -INFINITY) ? 0.f : rowmax;
   } else {
@@ -267,17 +283,19 @@ __device__ __forceinline__ void softmax_step(uint32_t (&sreg)[128], uint32_t tS,
         m_ref = rowmax;
         l *= alpha;
       }
-      // O_t is complete up to tile j-1 here: the commit that released S_t(j) was issued after it.
+      // O_t is complete up to tile j-1 here: the commit that released S_t(j) was issued after it (P over S), or
+      // the wait above has seen it (SEP_P).
       rescale_o_row<HD>(tO, alpha);
     }
   }
   const float negm = CFG::PSHIFT - m_ref * sl;
   if constexpr (PT == kDtBF16) {
-    if (split) l += emit_p<128, PT, EMU, true>(sreg, tS, tS + 64, sl, negm);
-    else l += emit_p<128, PT, EMU, false, true>(sreg, tS, 0u, sl, negm, bar_half);
+    if (split) l += emit_p<128, PT, EMU, true>(sreg, tP, tS + 64, sl, negm);
+    else l += emit_p<128, PT, EMU, false, true>(sreg, tP, 0u, sl, negm, bar_half);
   } else {
-    l += emit_p<128, PT, EMU, false, true>(sreg, tS, 0u, sl, negm, bar_half);
+    l += emit_p<128, PT, EMU, false, true>(sreg, tP, 0u, sl, negm, bar_half);
   }
+  return true;
 }
 
 // O_t (fp32, tensor memory) * inv -> 16 bit -> shared-memory tile in the 128-byte swizzled layout the TMA
