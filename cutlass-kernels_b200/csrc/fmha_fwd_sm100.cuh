@@ -53,10 +53,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_p_full = bar_s_full + 16;               // [2][2]: per tile, P of keys 0-63 / of keys 64-127
   const uint32_t bar_o_full = bar_p_full + 32;               // [2]
   const uint32_t bar_o_staged = bar_o_full + 16;             // [2]
-  const uint32_t bar_s_read = bar_o_staged + 16;             // [2] SEP_P: S_t is in the softmax registers (4 warps)
-  const uint32_t bar_pv_done = bar_s_read + 16;              // [2] SEP_P: O_t += P_t V_j is complete
+  const uint32_t bar_pv_done = bar_o_staged + 16;            // [2] SEP_P: O_t += P_t V_j is complete
   const uint32_t off_misc = (bar_pv_done + 16) - sBar;
-  static_assert(8 + 16 * C::NSLOT + 16 + 32 + 16 + 16 + 16 + 16 + 16 <= C::BARB, "barrier block overflows");
+  static_assert(8 + 16 * C::NSLOT + 16 + 32 + 16 + 16 + 16 + 16 <= C::BARB, "barrier block overflows");
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gBar + off_misc + 4);
   const AbortCtx actx{s_abort, p.status};
@@ -115,7 +114,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_p_full + 16 * t + 8, 4);
       mbar_init(bar_o_full + 8 * t, 1);
       mbar_init(bar_o_staged + 8 * t, 128);
-      mbar_init(bar_s_read + 8 * t, 4);
       mbar_init(bar_pv_done + 8 * t, 1);
     }
     *s_abort = 0u;
@@ -143,11 +141,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (p.causal) { const int v0 = qblk * 256 + diag_off + 1; visible = v0 < visible ? v0 : visible; }
     split = visible < p.split_keys;
   }
-  // How far Q K^T runs ahead of P V for one query tile.  With P over S (1) the scores of key tile j+1 are computed
-  // after P_j V_j has consumed P.  With buffers of its own for P (2) Q K_{j+1}^T is issued as soon as the softmax
-  // warps hold S_j in registers, so S_{j+1} is there long before they have finished tile j.  The two-term P keeps
-  // its second term in the upper half of S and therefore the first order.
-  const int ahead = (C::SEP_P && !split) ? 2 : 1;
+  // When Q K_{j+1}^T of a query tile is issued.  With P over S: after P_j V_j has consumed P.  With buffers of its own
+  // for P: as soon as the first half of P_j has arrived (S_j has then long been read into registers), between the two
+  // halves of P_j V_j, so that S_{j+1} is complete before the softmax warps have finished tile j.  The two-term P
+  // keeps its second term in the upper half of S and therefore the first order.
+  const bool qk_early = C::SEP_P && !split;
 
   if (warp >= 8) {
    // Third warpgroup: hands most of its registers to the softmax warpgroups.
@@ -159,7 +157,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive_expect_tx(bar_q_full, q_bytes);
       for (int t = 0; t < 2; ++t)
         if (n_of(t) > 0) tma_load_5d(sQ + t * C::TILEB, &tm_q, bar_q_full, 0, qblk * 256 + t * 128, 0, head, batch);
-      // Tiles enter the ring in the order the UMMA warp consumes them: K_0 (.. K_{ahead-1}), then V_j, K_{j+ahead}.
+      // Tiles enter the ring in the order the UMMA warp consumes them: K_0, then V_j, K_{j+1}.
       int idx = 0;
       bool ok = true;
       auto load_tile = [&](bool is_v, int j) {
@@ -170,10 +168,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive_expect_tx(bar_kv_full + 8 * slot, is_v ? C::VTILEB : C::TILEB);
         tma_load_5d(sRing + slot * C::SLOTB, is_v ? &tm_v : &tm_k, bar_kv_full + 8 * slot, 0, j * C::BN, 0, head, batch);
       };
-      for (int j = 0; j < ahead && j < n_kv && ok; ++j) load_tile(false, j);
+      load_tile(false, 0);
       for (int j = 0; j < n_kv && ok; ++j) {
         load_tile(true, j);
-        if (j + ahead < n_kv && ok) load_tile(false, j + ahead);
+        if (j + 1 < n_kv && ok) load_tile(false, j + 1);
       }
     }
    } else if (warp == 8) {
@@ -222,48 +220,40 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       };
 
-      // The ring is consumed in the producer's order: K_0 (.. K_{ahead-1}), then V_j, K_{j+ahead}.
-      int idx = 0;
-      auto next_slot = [&](int& slot, uint32_t& ph) {
-        slot = idx % C::NSLOT;
-        ph = (uint32_t)(idx / C::NSLOT) & 1u;
-        ++idx;
-      };
       CFK_PROF_DECL(4)
       ok = mbar_wait_warp(bar_q_full, 0, actx, kErrFmhaQFull);
-      // Q K_j^T for j < ahead: the first needs nothing but its operands, the second (SEP_P) that S_0 has been read
-      for (int j = 0; j < ahead && j < n_kv && ok; ++j) {
-        int kslot;
-        uint32_t kph;
-        next_slot(kslot, kph);
-        ok = mbar_wait_warp(bar_kv_full + 8 * kslot, kph, actx, kErrFmhaKvFull);
-        CFK_PROF_MARK(0)
-        if (!ok) break;
+      if (ok) ok = mbar_wait_warp(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
+      CFK_PROF_MARK(0)
+      if (ok) {
         tc_fence_after_sync();
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_of(t)) continue;
-          if (j > 0) {
-            ok = mbar_wait_warp(bar_s_read + 8 * t, (uint32_t)(j - 1) & 1u, actx, kErrFmhaSRead);
-            if (!ok) break;
+        for (int t = 0; t < 2; ++t)
+          if (n_of(t) > 0) {
+            issue_qk(t, 0);
+            umma_commit_e<false>(bar_s_full + 8 * t, leader);
+          }
+        umma_commit_e<false>(bar_kv_empty + 0, leader);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int vidx = 2 * j + 1, kidx = 2 * j + 2;
+        const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
+        CFK_PROF_MARK(3)
+        ok = mbar_wait_warp(bar_kv_full + 8 * vslot, (vidx / C::NSLOT) & 1, actx, kErrFmhaKvFull);
+        CFK_PROF_MARK(1)
+        bool k_ready = false;
+        // S_t = Q_t K_{j+1}^T
+        auto next_qk = [&](int t) -> bool {
+          if (!k_ready) {
+            if (!mbar_wait_warp(bar_kv_full + 8 * kslot, (kidx / C::NSLOT) & 1, actx, kErrFmhaKvFull)) return false;
             tc_fence_after_sync();
+            k_ready = true;
           }
           issue_qk(t, kslot);
           umma_commit_e<false>(bar_s_full + 8 * t, leader);
-        }
-        if (ok) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        int vslot, kslot = 0;
-        uint32_t vph, kph = 0;
-        next_slot(vslot, vph);
-        const bool have_k = j + ahead < n_kv;
-        if (have_k) next_slot(kslot, kph);
-        CFK_PROF_MARK(3)
-        ok = mbar_wait_warp(bar_kv_full + 8 * vslot, vph, actx, kErrFmhaKvFull);
-        CFK_PROF_MARK(1)
-        bool k_ready = false;
+          return true;
+        };
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_of(t)) continue;
+          const bool more = j + 1 < n_of(t);
           CFK_PROF_MARK(3)
           // with the two-term P the first-half barrier is not signalled; everything waits for the second
           if (!split) {
@@ -271,6 +261,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (!ok) break;
             tc_fence_after_sync();
             issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
+            if (qk_early && more) {
+              ok = next_qk(t);
+              if (!ok) break;
+            }
           }
           ok = mbar_wait_warp(bar_p_full + 16 * t + 8, j & 1, actx, kErrFmhaPFull);
           CFK_PROF_MARK(2)
@@ -284,25 +278,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             issue_pv_half(t, vslot, 1, 1u);
           }
           if constexpr (C::SEP_P) umma_commit_e<false>(bar_pv_done + 8 * t, leader);
-          if (j == n_of(t) - 1) umma_commit_e<false>(bar_o_full + 8 * t, leader);
-          if (j + ahead < n_of(t)) {
-            if (ahead == 2) {   // the softmax warps hold S_t(j+1) in registers: its buffer may take S_t(j+2)
-              ok = mbar_wait_warp(bar_s_read + 8 * t, (uint32_t)(j + 1) & 1u, actx, kErrFmhaSRead);
-              if (!ok) break;
-            }
-            if (!k_ready) {
-              ok = mbar_wait_warp(bar_kv_full + 8 * kslot, kph, actx, kErrFmhaKvFull);
-              if (!ok) break;
-              k_ready = true;
-            }
-            tc_fence_after_sync();
-            issue_qk(t, kslot);
-            umma_commit_e<false>(bar_s_full + 8 * t, leader);
+          if (!more) umma_commit_e<false>(bar_o_full + 8 * t, leader);
+          if (!qk_early && more) {
+            ok = next_qk(t);
+            if (!ok) break;
           }
         }
         if (ok) {
           umma_commit_e<false>(bar_kv_empty + 8 * vslot, leader);
-          if (have_k) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
+          if (j + 1 < n_kv) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
         }
       }
       CFK_PROF_MARK(3)
@@ -351,10 +335,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (j > 0) pv_seen = mbar_test_wait(bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u);
       }
       tmem_wait_ld();
-      if constexpr (C::SEP_P) {   // S_t may take the scores of the next key tile
-        tc_fence_before_sync();
-        mbar_arrive_warp(bar_s_read + 8 * t);
-      }
       CFK_PROF_MARK(1)
 
       if constexpr (DUMP) dump_scores(p, sreg, batch, head, row_g, j * C::BN);

@@ -9,7 +9,7 @@ constexpr int kDtF16 = 0, kDtBF16 = 1, kDtE4M3 = 2;
 constexpr int kErrFmhaQFull = 101, kErrFmhaKvFull = 102, kErrFmhaKvEmpty = 103, kErrFmhaSFull = 104,
               kErrFmhaPFull = 105, kErrFmhaOFull = 106, kErrFmhaOStaged = 107, kErrFmhaSFree = 108,
               kErrFmhaPvDone = 109, kErrFmhaMaxPub = 110, kErrFmhaPvDone256 = 111, kErrFmhaRowMax = 112,
-              kErrFmhaSRead = 113, kErrFmhaOFree = 115, kErrFmhaStats = 117, kErrFmhaCorrPv = 118;
+              kErrFmhaOFree = 115, kErrFmhaStats = 117, kErrFmhaCorrPv = 118;
 
 struct FmhaParams {
   int B, H, Sq, Skv;
