@@ -260,11 +260,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = mbar_wait_warp(bar_p_full + 16 * t, j & 1, actx, kErrFmhaPFull);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
-            if (qk_early && more) {
+            if (qk_early && more) {   // first: the softmax warps will ask for S before they ask for O
               ok = next_qk(t);
               if (!ok) break;
             }
+            issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
           }
           ok = mbar_wait_warp(bar_p_full + 16 * t + 8, j & 1, actx, kErrFmhaPFull);
           CFK_PROF_MARK(2)
