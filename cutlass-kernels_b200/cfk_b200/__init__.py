@@ -23,7 +23,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARG", 2: "UNSUPPORTED", 3: "DESCRIPTOR", 4:
 EXPORTS = ["cfk_fmha_forward", "cfk_fmha_forward_static", "cfk_gemm", "cfk_fill", "cfk_convert", "cfk_device_status",
            "cfk_last_cuda_error", "cfk_version", "cfk_selftest_umma", "cfk_umma_peak", "cfk_selftest_wait_gives_up", "cfk_selftest_wait_gives_up_static", "cfk_set_tunable", "cfk_get_tunable"]
 
-TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL, TUNE_FMHA_GRID = 0, 1, 2, 3
+TUNE_FMHA_EXP_EMU, TUNE_FMHA_GROUP_MB, TUNE_FMHA_KERNEL, TUNE_FMHA_GRID, TUNE_FMHA_SCHED = 0, 1, 2, 3, 4
 
 
 class FmhaArgs(C.Structure):

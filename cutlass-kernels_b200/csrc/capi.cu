@@ -161,16 +161,18 @@ __global__ void convert_kernel(const void* src, int sdt, void* dst, int ddt, int
 
 // Tunables (process-wide).  Defaults are the measured best on B200.
 // EXP_EMU -1 = by type: 1 of 4 pairs for 16-bit inputs, 2 of 4 for e4m3 (measured best on B200).
-static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64, 0, 0};
-static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}, {0}, {0}};
+// SCHED -1 = by type (see fmha_prepare).
+static const int kTunableDefault[CFK_TUNE_COUNT] = {-1, 64, 0, 0, -1};
+static std::atomic<int> g_tunable[CFK_TUNE_COUNT] = {{-1}, {64}, {0}, {0}, {-1}};
 
 // The knobs can also be set from the environment (CFK_TUNE_FMHA_EXP_EMU, CFK_TUNE_FMHA_GROUP_MB, CFK_TUNE_FMHA_KERNEL,
-// CFK_TUNE_FMHA_GRID), read once before the first FMHA call: the command-line drivers have no flags for them.
+// CFK_TUNE_FMHA_GRID, CFK_TUNE_FMHA_SCHED), read once before the first FMHA call: the command-line drivers have no flags for them.
 static void tunables_from_env() {
   static std::once_flag once;
   std::call_once(once, [] {
     static const char* const names[CFK_TUNE_COUNT] = {"CFK_TUNE_FMHA_EXP_EMU", "CFK_TUNE_FMHA_GROUP_MB",
-                                                      "CFK_TUNE_FMHA_KERNEL", "CFK_TUNE_FMHA_GRID"};
+                                                      "CFK_TUNE_FMHA_KERNEL", "CFK_TUNE_FMHA_GRID",
+                                                      "CFK_TUNE_FMHA_SCHED"};
     for (int i = 0; i < CFK_TUNE_COUNT; ++i) {
       const char* v = std::getenv(names[i]);
       if (v && *v) (void)cfk_set_tunable(i, std::atoi(v));
@@ -192,6 +194,7 @@ extern "C" int cfk_set_tunable(int which, int value) {
   if (which == CFK_TUNE_FMHA_EXP_EMU && value > 3) return CFK_ERR_INVALID_ARG;
   if (which == CFK_TUNE_FMHA_GROUP_MB && (value < 1 || value > 1024)) return CFK_ERR_INVALID_ARG;
   if (which == CFK_TUNE_FMHA_KERNEL && value > 2) return CFK_ERR_INVALID_ARG;
+  if (which == CFK_TUNE_FMHA_SCHED && value > 1) return CFK_ERR_INVALID_ARG;
   g_tunable[which].store(value);
   return CFK_OK;
 }
@@ -317,6 +320,13 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   p.out_bf16 = a->out_dtype == CFK_BF16;
   // one 128-row tile per CTA at head dimension 256 and in the persistent kernel, two side by side otherwise
   p.nqblk = (a->head_dim == 256 || L.variant == 2) ? (a->seqlen_q + 127) / 128 : (a->seqlen_q + 255) / 256;
+  {
+    // Default by input type, the measured best: with e4m3 Q and K the first GEMM is short enough for the two query
+    // tiles to take turns on one score buffer (+2-4 % on every e4m3 shape); with 16-bit inputs the hand-over of
+    // the buffer would set the pace (c3 1246 -> 1221 TFLOP/s).
+    const int sched = g_tunable[CFK_TUNE_FMHA_SCHED].load();
+    p.sched = sched < 0 ? (a->dtype == CFK_E4M3 ? 1 : 0) : sched;
+  }
   p.split_keys = a->dtype == CFK_BF16 ? (a->p_split_keys < 0 ? 1024 : a->p_split_keys) : 0;
   p.scale_log2 = a->softmax_scale * 1.4426950408889634f * qd * kd;
   p.out_scale = vd;

@@ -53,9 +53,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t bar_p_full = bar_s_full + 16;               // [2][2]: per tile, P of keys 0-63 / of keys 64-127
   const uint32_t bar_o_full = bar_p_full + 32;               // [2]
   const uint32_t bar_o_staged = bar_o_full + 16;             // [2]
-  const uint32_t bar_pv_done = bar_o_staged + 16;            // [2] SEP_P: O_t += P_t V_j is complete
-  const uint32_t off_misc = (bar_pv_done + 16) - sBar;
-  static_assert(8 + 16 * C::NSLOT + 16 + 32 + 16 + 16 + 16 + 16 <= C::BARB, "barrier block overflows");
+  const uint32_t bar_pv_done = bar_o_staged + 16;            // [2] P in its own buffer: O_t += P_t V_j is complete
+  const uint32_t bar_s_read = bar_pv_done + 16;              // [2] shared S buffer: tile t's scores are in registers (4 warps)
+  const uint32_t off_misc = (bar_s_read + 16) - sBar;
+  static_assert(8 + 16 * C::NSLOT + 16 + 32 + 16 + 16 + 16 + 16 + 16 <= C::BARB, "barrier block overflows");
   volatile uint32_t* s_tmem_base = reinterpret_cast<volatile uint32_t*>(gBar + off_misc);
   volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(gBar + off_misc + 4);
   const AbortCtx actx{s_abort, p.status};
@@ -115,6 +116,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar_o_full + 8 * t, 1);
       mbar_init(bar_o_staged + 8 * t, 128);
       mbar_init(bar_pv_done + 8 * t, 1);
+      mbar_init(bar_s_read + 8 * t, 4);
     }
     *s_abort = 0u;
     fence_barrier_init();
@@ -141,11 +143,25 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (p.causal) { const int v0 = qblk * 256 + diag_off + 1; visible = v0 < visible ? v0 : visible; }
     split = visible < p.split_keys;
   }
-  // When Q K_{j+1}^T of a query tile is issued.  With P over S: after P_j V_j has consumed P.  With buffers of its own
-  // for P: as soon as the first half of P_j has arrived (S_j has then long been read into registers), between the two
-  // halves of P_j V_j, so that S_{j+1} is complete before the softmax warps have finished tile j.  The two-term P
-  // keeps its second term in the upper half of S and therefore the first order.
-  const bool qk_early = C::SEP_P && !split;
+  // Three schedules, one per CTA:
+  //  kOverS   P_t is written over S_t; Q_t K_{j+1}^T is issued after P_t(j) V_j has consumed P.  The two-term bf16 P
+  //           (second term in the upper half of S_t) needs this one.
+  //  kSepP    d = 64 leaves 128 columns of tensor memory free: P_t has a buffer of its own, and Q_t K_{j+1}^T is
+  //           issued as soon as the first half of P_t(j) has arrived (S_t(j) has then long been read into registers),
+  //           so S_t(j+1) is complete before the softmax warps have finished tile j.
+  //  kSharedS d = 128 has no column to spare, but one S buffer is enough for both query tiles if the tiles take
+  //           turns: S lives in it only from the Q K^T to the tcgen05.ld of the softmax warps, P_0 and P_1 take the
+  //           columns of the second S buffer, and again no Q K^T waits for a P V.  Entries (tile, key tile) pass
+  //           through the buffer in the order (0,0) (1,0) (0,1) (1,1) ..; the UMMA warp runs three entries ahead
+  //           of the P V it issues.
+  constexpr int kOverS = 0, kSepP = 1, kSharedS = 2;
+  int mode = kOverS;
+  if (!split) {
+    if (C::SEP_P) mode = kSepP;
+    else if (p.sched == 1 && n_t0 > 0 && n_t1 > 0) mode = kSharedS;
+  }
+  const bool qk_early = mode == kSepP;
+  const uint32_t p_col0 = mode == kSepP ? C::P_COL0 : 128u;        // P_t at p_col0 + 64 t (kSepP, kSharedS)
 
   if (warp >= 8) {
    // Third warpgroup: hands most of its registers to the softmax warpgroups.
@@ -157,7 +173,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive_expect_tx(bar_q_full, q_bytes);
       for (int t = 0; t < 2; ++t)
         if (n_of(t) > 0) tma_load_5d(sQ + t * C::TILEB, &tm_q, bar_q_full, 0, qblk * 256 + t * 128, 0, head, batch);
-      // Tiles enter the ring in the order the UMMA warp consumes them: K_0, then V_j, K_{j+1}.
+      // Tiles enter the ring in the order the UMMA warp first uses them: K_0, then V_j, K_{j+1}.
       int idx = 0;
       bool ok = true;
       auto load_tile = [&](bool is_v, int j) {
@@ -168,10 +184,19 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive_expect_tx(bar_kv_full + 8 * slot, is_v ? C::VTILEB : C::TILEB);
         tma_load_5d(sRing + slot * C::SLOTB, is_v ? &tm_v : &tm_k, bar_kv_full + 8 * slot, 0, j * C::BN, 0, head, batch);
       };
-      load_tile(false, 0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        load_tile(true, j);
-        if (j + 1 < n_kv && ok) load_tile(false, j + 1);
+      if (mode != kSharedS) {
+        load_tile(false, 0);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          load_tile(true, j);
+          if (j + 1 < n_kv && ok) load_tile(false, j + 1);
+        }
+      } else {   // K_0, K_1, then V_j, K_{j+2}
+        load_tile(false, 0);
+        if (n_kv > 1 && ok) load_tile(false, 1);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          load_tile(true, j);
+          if (j + 2 < n_kv && ok) load_tile(false, j + 2);
+        }
       }
     }
    } else if (warp == 8) {
@@ -189,7 +214,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_qk = [&](int t, int slot) {
         const uint64_t a0 = desc_advance_lo(aq0, t * C::TILEB);
         const uint64_t b0 = desc_advance_lo(bk0, slot * C::SLOTB);
-        const uint32_t d = tmem_base + t * 128;
+        const uint32_t d = tmem_base + (mode == kSharedS ? 0 : t * 128);
 #pragma unroll
         for (int kk = 0; kk < C::QK_KSTEPS; ++kk) {
           const uint32_t off = (kk / C::KSPS) * C::SUBB + (kk % C::KSPS) * 32;
@@ -201,7 +226,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_pv_half = [&](int t, int slot, int half, uint32_t accumulate) {
         const uint64_t b0 = desc_advance_lo(bv0, slot * C::SLOTB);
         const uint32_t d = tmem_base + C::O_COL0 + t * HD;
-        const uint32_t a = tmem_base + (C::SEP_P ? C::P_COL0 + t * 64 : t * 128);
+        const uint32_t a = tmem_base + (mode == kOverS ? t * 128 : p_col0 + t * 64);
 #pragma unroll
         for (int k2 = 0; k2 < C::PV_KSTEPS / 2; ++k2) {
           const int kk = half * (C::PV_KSTEPS / 2) + k2;
@@ -222,6 +247,59 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       CFK_PROF_DECL(4)
       ok = mbar_wait_warp(bar_q_full, 0, actx, kErrFmhaQFull);
+      if (mode == kSharedS) {
+        // Entry k of the S buffer is (tile, key tile) = (k & 1, k >> 1) while both tiles have key tiles left, then the
+        // rest of the longer one.  Ring index of K_j and V_j in the producer's order K_0 K_1 V_0 K_2 V_1 ..
+        const int n_lo = n_t0 < n_t1 ? n_t0 : n_t1, total = n_t0 + n_t1;
+        auto entry = [&](int k, int& t, int& j) {
+          if (k < 2 * n_lo) { t = k & 1; j = k >> 1; }
+          else { t = n_t0 > n_t1 ? 0 : 1; j = n_lo + (k - 2 * n_lo); }
+        };
+        auto idx_k = [&](int j) { return j < 2 ? j : 2 * j - 1; };
+        auto idx_v = [&](int j) { return j + 2 <= n_kv ? 2 * j + 2 : (n_kv == 1 ? 1 : 2 * n_kv - 1); };
+        // first / last entry that uses key tile j: tile 0's, tile 1's - or the only one
+        auto first_of = [&](int t, int j) { return t == 0 || j >= n_t0; };
+        auto last_of = [&](int t, int j) { return t == 1 || j >= n_t1; };
+        auto do_qk = [&](int k) -> bool {
+          int t, j;
+          entry(k, t, j);
+          const int idx = idx_k(j), slot = idx % C::NSLOT;
+          if (first_of(t, j) && !mbar_wait_warp(bar_kv_full + 8 * slot, (idx / C::NSLOT) & 1, actx, kErrFmhaKvFull))
+            return false;
+          if (k > 0) {   // the scores of the previous entry are in its owner's registers
+            int tp, jp;
+            entry(k - 1, tp, jp);
+            if (!mbar_wait_warp(bar_s_read + 8 * tp, (uint32_t)jp & 1u, actx, kErrFmhaSRead)) return false;
+          }
+          tc_fence_after_sync();
+          issue_qk(t, slot);
+          umma_commit_e<false>(bar_s_full + 8 * t, leader);
+          if (last_of(t, j)) umma_commit_e<false>(bar_kv_empty + 8 * slot, leader);
+          return true;
+        };
+        auto do_pv = [&](int k) -> bool {
+          int t, j;
+          entry(k, t, j);
+          const int idx = idx_v(j), slot = idx % C::NSLOT;
+          if (first_of(t, j) && !mbar_wait_warp(bar_kv_full + 8 * slot, (idx / C::NSLOT) & 1, actx, kErrFmhaKvFull))
+            return false;
+          if (!mbar_wait_warp(bar_p_full + 16 * t, j & 1, actx, kErrFmhaPFull)) return false;
+          tc_fence_after_sync();
+          issue_pv_half(t, slot, 0, j > 0 ? 1u : 0u);
+          if (!mbar_wait_warp(bar_p_full + 16 * t + 8, j & 1, actx, kErrFmhaPFull)) return false;
+          tc_fence_after_sync();
+          issue_pv_half(t, slot, 1, 1u);
+          umma_commit_e<false>(bar_pv_done + 8 * t, leader);
+          if (j == n_of(t) - 1) umma_commit_e<false>(bar_o_full + 8 * t, leader);
+          if (last_of(t, j)) umma_commit_e<false>(bar_kv_empty + 8 * slot, leader);
+          return true;
+        };
+        for (int k = 0; k < 3 && k < total && ok; ++k) ok = do_qk(k);
+        for (int k = 0; k < total && ok; ++k) {
+          ok = do_pv(k);
+          if (ok && k + 3 < total) ok = do_qk(k + 3);
+        }
+      } else {
       if (ok) ok = mbar_wait_warp(bar_kv_full + 0, 0, actx, kErrFmhaKvFull);   // K_0 is ring index 0
       CFK_PROF_MARK(0)
       if (ok) {
@@ -289,6 +367,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (j + 1 < n_kv) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
         }
       }
+      }
       CFK_PROF_MARK(3)
       CFK_PROF_FLUSH(8, 4, (leader != 0))
     }
@@ -299,8 +378,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int t = warp >> 2;               // query tile of this warpgroup
     const int r = tid & 127;               // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + t * 128;
-    const uint32_t tP = C::SEP_P ? tmem_base + lane_base + C::P_COL0 + t * 64 : tS;
+    const uint32_t tS = tmem_base + lane_base + (mode == kSharedS ? 0 : t * 128);
+    const uint32_t tP = mode == kOverS ? tS : tmem_base + lane_base + p_col0 + t * 64;
+    const bool own_p = mode != kOverS;     // P has a buffer of its own
     const uint32_t tO = tmem_base + lane_base + C::O_COL0 + t * HD;
     const int row_g = qblk * 256 + t * 128 + r;     // global query row
     const int n_my = n_of(t);
@@ -318,7 +398,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     CFK_PROF_DECL(8)
     for (int j = 0; j < n_my; ++j) {
       CFK_PROF_MARK(7)
-      if (!(C::SEP_P && __all_sync(0xffffffffu, s_seen)))   // SEP_P: looked at while the previous tile's P was on its way
+      if (!(own_p && __all_sync(0xffffffffu, s_seen)))   // own_p: looked at while the previous tile's P was on its way
         ok = mbar_wait_warp(bar_s_full + 8 * t, j & 1, actx, kErrFmhaSFull);
       CFK_PROF_MARK(0)
       if (!ok) break;
@@ -327,14 +407,16 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_x32(tS + 32, sreg + 32);
       tmem_ld_x32(tS + 64, sreg + 64);
       tmem_ld_x32(tS + 96, sreg + 96);
-      // SEP_P: an early look at "P V of the previous key tile is complete", used after the row maximum (measured:
+      // own_p: an early look at "P V of the previous key tile is complete", used after the row maximum (measured:
       // looking here, behind the loads, beats looking before them or only when the answer is needed, 824 against
       // 787 TFLOP/s at d = 64 fp16)
-      uint32_t pv_seen = (j > 0 && C::SEP_P) ? 0u : 1u;
-      if constexpr (C::SEP_P) {
-        if (j > 0) pv_seen = mbar_test_wait(bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u);
-      }
+      uint32_t pv_seen = 0u;
+      if (own_p && j > 0) pv_seen = mbar_test_wait(bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u);
       tmem_wait_ld();
+      if (mode == kSharedS) {   // the S buffer may take the other tile's scores
+        tc_fence_before_sync();
+        mbar_arrive_warp(bar_s_read + 8 * t);
+      }
       CFK_PROF_MARK(1)
 
       if constexpr (DUMP) dump_scores(p, sreg, batch, head, row_g, j * C::BN);
@@ -343,13 +425,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }
         ok = softmax_step<C, PT, HD, EMU>(sreg, tS, tP, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim, lim - j * C::BN,
-                                          split, bar_p_full + 16 * t, bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u, pv_seen,
-                                          actx, m_ref, m_true, l);
+                                          split, bar_p_full + 16 * t, own_p ? bar_pv_done + 8 * t : 0u,
+                                          (uint32_t)(j - 1) & 1u, pv_seen, actx, m_ref, m_true, l);
         if (!ok) break;
       }
       CFK_PROF_MARK(3)
-      // SEP_P: the scores of the next key tile are as a rule complete by now; the look overlaps the wait for the stores
-      if constexpr (C::SEP_P) s_seen = mbar_test_wait(bar_s_full + 8 * t, (uint32_t)(j + 1) & 1u);
+      // own_p: the scores of the next key tile are as a rule complete by now; the look overlaps the wait for the stores
+      if (own_p) s_seen = mbar_test_wait(bar_s_full + 8 * t, (uint32_t)(j + 1) & 1u);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar_p_full + 16 * t + 8);

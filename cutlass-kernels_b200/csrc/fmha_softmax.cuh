@@ -243,12 +243,13 @@ __device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {
 
 // One key tile of the online softmax for the thread that owns a query row.  On entry sreg[0..127] holds
 // the row's raw scores (S_t, fp32 bits); on exit P has been written to tensor memory at tP (over S_t, or a buffer
-// of its own with SEP_P; tcgen05.st issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first
+// of its own; tcgen05.st issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first
 // key tile of the row; `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible
 // column.  `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory; not
 // used with the two-term P, whose second term goes to the upper half of S_t.
-// With SEP_P the S buffer no longer says that P V of the previous key tile has run (the next Q K^T was issued
-// before it), so the thread waits for `bar_pv_done` before it touches O_t or the P buffer again.  Returns false if
+// When P has a buffer of its own (`bar_pv_done` != 0) the S buffer no longer says that P V of the previous key tile
+// has run (the next Q K^T was issued before it), so the thread waits for `bar_pv_done` before it touches O_t or the
+// P buffer again.  Returns false if
 // that wait gave up.  A look at a barrier costs one to several hundred clocks even when the barrier is complete
 // (the tensor core's operand reads keep the shared-memory port busy), so the caller looks early, with a test that
 // cannot put the warp to sleep, and hands the answer in.
@@ -266,11 +267,9 @@ __device__ __forceinline__ bool softmax_step(uint32_t (&sreg)[128], uint32_t tS,
   }
   const float rowmax = row_max_n<128>(sreg);
   m_true = fmaxf(m_true, rowmax);
-  if constexpr (CFG::SEP_P) {
-    if (!first) {   // `pv_seen`: an early look (issued before the row maximum) already found it complete
-      if (!__all_sync(0xffffffffu, pv_seen) && !mbar_wait_warp(bar_pv_done, pv_parity, actx, kErrFmhaPvDone)) return false;
-      tc_fence_after_sync();
-    }
+  if (bar_pv_done != 0u && !first) {   // `pv_seen`: an early look (issued before the row maximum) found it complete
+    if (!__all_sync(0xffffffffu, pv_seen) && !mbar_wait_warp(bar_pv_done, pv_parity, actx, kErrFmhaPvDone)) return false;
+    tc_fence_after_sync();
   }
   if (first) {
     m_ref = (rowmax == -INFINITY) ? 0.f : rowmax;
@@ -284,7 +283,7 @@ __device__ __forceinline__ bool softmax_step(uint32_t (&sreg)[128], uint32_t tS,
         l *= alpha;
       }
       // O_t is complete up to tile j-1 here: the commit that released S_t(j) was issued after it (P over S), or
-      // the wait above has seen it (SEP_P).
+      // the wait above has seen it.
       rescale_o_row<HD>(tO, alpha);
     }
   }

@@ -174,9 +174,13 @@ const char* cfk_last_cuda_error(void);
  *                           128-row tile at a time, with the scores double-buffered, both softmax warpgroups on the
  *                           two halves of the same key tile and a correction warpgroup (head dimensions 64 and 128).
  *   CFK_TUNE_FMHA_GRID      kernel 2: CTAs of the persistent grid; 0 = one per SM.  Never more than work items.
+ *   CFK_TUNE_FMHA_SCHED     kernel 0 at head dimension 128: how the two query tiles of a CTA use tensor memory.
+ *                           0: each has a score buffer and writes its probabilities over it; 1: they take turns on
+ *                           one score buffer and keep their probabilities in buffers of their own, so that no
+ *                           Q K^T waits for a P V; -1 (default): by input type, the measured best.
  */
 enum cfk_tunable { CFK_TUNE_FMHA_EXP_EMU = 0, CFK_TUNE_FMHA_GROUP_MB = 1, CFK_TUNE_FMHA_KERNEL = 2, CFK_TUNE_FMHA_GRID = 3,
-                   CFK_TUNE_COUNT = 4 };
+                   CFK_TUNE_FMHA_SCHED = 4, CFK_TUNE_COUNT = 5 };
 int cfk_set_tunable(int which, int value);
 int cfk_get_tunable(int which); /* -1 for an unknown knob */
 
