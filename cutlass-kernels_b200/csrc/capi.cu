@@ -322,7 +322,8 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   p.nqblk = (a->head_dim == 256 || L.variant == 2) ? (a->seqlen_q + 127) / 128 : (a->seqlen_q + 255) / 256;
   {
     // Default by input type, the measured best: with e4m3 Q and K the first GEMM is short enough for the two query
-    // tiles to take turns on one score buffer (+2-4 % on every e4m3 shape); with 16-bit inputs the hand-over of
+    // tiles to take turns on one score buffer (+8-12 % on every e4m3 shape together with the share of exponentials on
+    // the FMA pipe that goes with it, below); with 16-bit inputs the hand-over of
     // the buffer would set the pace (c3 1246 -> 1221 TFLOP/s).
     const int sched = g_tunable[CFK_TUNE_FMHA_SCHED].load();
     p.sched = sched < 0 ? (a->dtype == CFK_E4M3 ? 1 : 0) : sched;
@@ -334,7 +335,8 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   p.s_dump = a->s_dump; p.s_dump_bf16 = a->dtype == CFK_BF16;
   L.iterations = a->iterations;
   L.exp_emu = g_tunable[CFK_TUNE_FMHA_EXP_EMU].load();
-  if (L.exp_emu < 0) L.exp_emu = a->dtype == CFK_E4M3 ? 2 : 1;
+  // e4m3 at d = 128 on the shared score buffer: 1 of 4 (c5 1631 against 1486 TFLOP/s with 2 of 4 and 1386 with none)
+  if (L.exp_emu < 0) L.exp_emu = a->dtype != CFK_E4M3 ? 1 : (a->head_dim == 128 && L.variant == 0 && p.sched == 1) ? 1 : 2;
   {
     // Causal: CTAs differ in length, so heads are interleaved (heaviest blocks of a group of heads first);
     // the group is sized so that its K and V stay in L2.  Non-causal: one head at a time.

@@ -85,16 +85,18 @@ def test_fmha_schedule_large_logits_trigger_rescale(sched_lib, oracle, cuda, cau
 
 @pytest.mark.parametrize("dtype,causal", [(0, False), (0, True), (1, True), (2, False), (2, True)])
 def test_fmha_schedules_agree_bit_for_bit(lib, cuda, dtype, causal):
-    from cfk_b200 import TUNE_FMHA_SCHED
+    from cfk_b200 import TUNE_FMHA_EXP_EMU, TUNE_FMHA_SCHED
     low, _, scales = make_qkv(dtype, 2, 1536, 1536, 4, 128, seed=77)
     outs = []
     try:
+        lib.set_tunable(TUNE_FMHA_EXP_EMU, 1)      # its default depends on the schedule; the arithmetic must not
         for sched in (0, 1):
             lib.set_tunable(TUNE_FMHA_SCHED, sched)
             o, stats = run_fmha(lib, low, scales, dtype, causal)
             outs.append((o, stats))
     finally:
         lib.set_tunable(TUNE_FMHA_SCHED, -1)
+        lib.set_tunable(TUNE_FMHA_EXP_EMU, -1)
     assert np.array_equal(outs[0][0], outs[1][0])
     for name in outs[0][1]:
         assert np.array_equal(outs[0][1][name], outs[1][1][name]), name
