@@ -165,7 +165,8 @@ const char* cfk_last_cuda_error(void);
  * restores the default.  No counterpart in the reference, whose knobs are compile-time macros
  * (src/fmha-pipeline/shared_storage.h:3-32).
  *   CFK_TUNE_FMHA_EXP_EMU   0..3: of every four pairs of softmax exponentials, how many are evaluated
- *                           with a cubic on the FMA pipe instead of the special-function unit.
+ *                           with a cubic on the FMA pipe instead of the special-function unit.  -1 (default):
+ *                           by input type and head dimension, the measured best.
  *   CFK_TUNE_FMHA_GROUP_MB  causal only: heads are scheduled in groups whose K and V total at most
  *                           this many MiB (so they share L2), heaviest query blocks first.
  *   CFK_TUNE_FMHA_KERNEL    which FMHA kernel runs: 0 one CTA per 256 query rows (two 128-row tiles side by side);
