@@ -14,7 +14,8 @@
 //
 // Two 128-row query tiles are in flight per CTA so that the tensor core works on one tile's GEMMs
 // while the other tile's softmax runs.  P (unnormalised, rounded to the GEMM-II operand type exactly
-// as fmha_consumer.h:54 does) is written back over S in TMEM and consumed from there; V is used in
+// as fmha_consumer.h:54 does) is written to TMEM - over S, or into a buffer of its own where the columns
+// allow it (the three schedules are described where `mode` is set) - and consumed from there; V is used in
 // its natural [key][d] layout through an MN-major operand descriptor, so neither the host-side V
 // transpose (src/fmha-pipeline/fmha_forward.cu:514-532) nor the register shuffle of reg2reg.h:45-108
 // exists here.  The running maximum is only moved (and O only rescaled) when the new maximum exceeds
@@ -355,7 +356,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           } else {
             issue_pv_half(t, vslot, 1, 1u);
           }
-          if constexpr (C::SEP_P) umma_commit_e<false>(bar_pv_done + 8 * t, leader);
+          if (mode == kSepP) umma_commit_e<false>(bar_pv_done + 8 * t, leader);
           if (!more) umma_commit_e<false>(bar_o_full + 8 * t, leader);
           if (!qk_early && more) {
             ok = next_qk(t);
