@@ -336,7 +336,11 @@ int cfk::fmha_prepare(const cfk_fmha_args* a, FmhaLaunch* out, int* p_dtype) {
   L.iterations = a->iterations;
   L.exp_emu = g_tunable[CFK_TUNE_FMHA_EXP_EMU].load();
   // e4m3 at d = 128 on the shared score buffer: 1 of 4 (c5 1631 against 1486 TFLOP/s with 2 of 4 and 1386 with none)
-  if (L.exp_emu < 0) L.exp_emu = a->dtype != CFK_E4M3 ? 1 : (a->head_dim == 128 && L.variant == 0 && p.sched == 1) ? 1 : 2;
+  // 16-bit at d = 256 (one softmax warpgroup, tensor-bound): none (fp16 1302 / 1266 / 1224 / 1195 for 0..3 of 4)
+  if (L.exp_emu < 0) {
+    if (a->dtype != CFK_E4M3) L.exp_emu = a->head_dim == 256 ? 0 : 1;
+    else L.exp_emu = (a->head_dim == 128 && L.variant == 0 && p.sched == 1) ? 1 : 2;
+  }
   {
     // Causal: CTAs differ in length, so heads are interleaved (heaviest blocks of a group of heads first);
     // the group is sized so that its K and V stay in L2.  Non-causal: one head at a time.
