@@ -68,6 +68,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_r, int tiles_c, 
   t -= band * band_tiles;
   tr = first_r + t % rows_in_band;
   tc = t / rows_in_band;
+  if (band & 1) tc = tiles_c - 1 - tc;   // back and forth: a band starts on the Y panels the band before it ended on
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
@@ -122,12 +123,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CU
 
   if (warp == 0) {
     if (lane == 0) {
-      int idx = 0;
+      int idx = 0, local = 0;
       bool ok = true;
-      for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs) {
+      for (int tile = pair_id; tile < total_tiles && ok; tile += n_pairs, ++local) {
         int tr, tc, b;
         tile_coords(tile, p.tiles_r, p.tiles_c, tr, tc, b);
-        for (int kb = 0; kb < nkb; ++kb, ++idx) {
+        // Every other tile of a pair walks the reduction backwards: its first k-blocks are the ones the tile before
+        // it (same row panels, as a rule) touched last, which are the ones still in L2.  The sum does not care.
+        for (int i = 0; i < nkb; ++i, ++idx) {
+          const int kb = (local & 1) ? nkb - 1 - i : i;
           const int s = idx % C::NSTAGE;
           const uint32_t ph = (idx / C::NSTAGE) & 1;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, actx, kErrGemmEmpty)) { ok = false; break; }
