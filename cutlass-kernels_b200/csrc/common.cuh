@@ -99,7 +99,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const A
     }
   }
 }
-// Same, with a warp-uniform verdict (needed before warp-collective tcgen05.ld/st).
+// Same, with a warp-uniform answer (needed before warp-collective tcgen05.ld/st).
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const AbortCtx& ctx, int where,
                                                unsigned backoff_ns = 0) {
   const bool ok = mbar_wait(bar, parity, ctx, where, kWaitLimitNs, backoff_ns);
@@ -363,7 +363,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // The skip decision of a CTA pair (see cta_should_skip), taken ONCE for the pair: if each CTA read the status word
 // for itself, another CTA's wait could give up between the two reads, one CTA of the pair would return and its peer
 // would go on to allocate tensor memory for the pair (which has no time limit) and to signal barriers in the shared
-// memory of a CTA that is gone.  Rank 0 reads the word and stores the verdict into both CTAs' shared memory; after
+// memory of a CTA that is gone.  Rank 0 reads the word and stores the decision into both CTAs' shared memory; after
 // the cluster barrier both branch on their own copy.  Every thread of both CTAs must call this.
 __device__ __forceinline__ bool pair_should_skip(const int* status) {
   __shared__ uint32_t s_pair_skip;
