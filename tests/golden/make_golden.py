@@ -44,6 +44,19 @@ def main():
                     f"{tag}_causal": np.int32(causal), f"{tag}_o": r["o"].astype(np.float32),
                     f"{tag}_lse": r["lse"].astype(np.float32)})
     np.savez_compressed(os.path.join(HERE, "attention_small.npz"), **out)
+    # head dimension 128 (the benchmark's), in a file of its own so that the file above keeps its bytes: a causal case
+    # whose two query tiles see different numbers of key tiles, and a causal case with an offset diagonal, a ragged
+    # last tile and a query block with one tile only
+    rng128 = np.random.default_rng(3082)
+    d128 = {}
+    for tag, (B, Sq, Skv, H, D, causal) in {"causal128": (1, 256, 256, 1, 128, True), "offset128": (1, 130, 333, 1, 128, True)}.items():
+        q, k, v = rounded(rng128, (B, Sq, H, D)), rounded(rng128, (B, Skv, H, D)), rounded(rng128, (B, Skv, H, D))
+        scale = 1.0 / math.sqrt(D)
+        r = attention_f64(q, k, v, scale, causal)
+        d128.update({f"{tag}_q": q.astype(np.float16), f"{tag}_k": k.astype(np.float16), f"{tag}_v": v.astype(np.float16),
+                     f"{tag}_scale": np.float32(scale), f"{tag}_causal": np.int32(causal), f"{tag}_o": r["o"].astype(np.float32),
+                     f"{tag}_lse": r["lse"].astype(np.float32)})
+    np.savez_compressed(os.path.join(HERE, "attention_d128.npz"), **d128)
     a = rng.uniform(-1, 1, (48, 80)).astype(np.float16).astype(np.float32)
     b = rng.uniform(-1, 1, (40, 80)).astype(np.float16).astype(np.float32)
     c_in = rng.uniform(-1, 1, (48, 40)).astype(np.float16).astype(np.float32)

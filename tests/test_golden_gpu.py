@@ -1,5 +1,6 @@
 """The CUDA path on the committed fixtures (tests/golden/*.npz, made by tests/golden/make_golden.py from the float64
-restatement of the reference's checker): the cases whose head dimension the kernels are built for, and the GEMM case.
+restatement of the reference's checker): the cases whose head dimension the kernels are built for (64 in attention_small.npz, 128 in attention_d128.npz), and
+the GEMM case.
 Same inputs, bit for bit, as the CPU test of the oracle on these files (test_oracle_cpu.py)."""
 import os
 
@@ -30,6 +31,30 @@ def test_fmha_on_the_golden_vectors(lib, cuda, tag, kernel):
     finally:
         lib.set_tunable(TUNE_FMHA_KERNEL, -1)
     assert np.abs(o.float().cpu().numpy() - data[f"{tag}_o"]).max() <= 2e-3        # the stated 16-bit bound
+    assert np.abs(lse.cpu().numpy() - data[f"{tag}_lse"]).max() <= 2e-3
+
+
+@pytest.mark.parametrize("tag", ["causal128", "offset128"])
+@pytest.mark.parametrize("kernel,sched", [(0, 0), (0, 1), (2, -1)])
+def test_fmha_on_the_golden_vectors_at_head_dimension_128(lib, cuda, tag, kernel, sched):
+    """The benchmark's head dimension: the two-tile kernel under both tensor-memory schedules and the persistent one."""
+    from cfk_b200 import TUNE_FMHA_KERNEL, TUNE_FMHA_SCHED
+    data = np.load(os.path.join(GOLDEN, "attention_d128.npz"))
+    q, k, v = (torch.from_numpy(data[f"{tag}_{n}"]).cuda() for n in "qkv")        # fp16, as stored
+    B, Sq, H, D = q.shape
+    Skv = k.shape[1]
+    o = torch.full((B, Sq, H, D), -1.0, device="cuda", dtype=torch.float16)
+    lse = torch.full((B, H, Sq), -1.0, device="cuda", dtype=torch.float32)
+    lib.set_tunable(TUNE_FMHA_KERNEL, kernel)
+    lib.set_tunable(TUNE_FMHA_SCHED, sched)
+    try:
+        lib.fmha_forward(q, k, v, o, dtype=0, batch=B, heads=H, seqlen_q=Sq, seqlen_kv=Skv, head_dim=D,
+                         softmax_scale=float(data[f"{tag}_scale"]), causal=bool(data[f"{tag}_causal"]), lse=lse)
+        lib.check_device()
+    finally:
+        lib.set_tunable(TUNE_FMHA_KERNEL, -1)
+        lib.set_tunable(TUNE_FMHA_SCHED, -1)
+    assert np.abs(o.float().cpu().numpy() - data[f"{tag}_o"]).max() <= 2e-3
     assert np.abs(lse.cpu().numpy() - data[f"{tag}_lse"]).max() <= 2e-3
 
 

@@ -110,6 +110,12 @@ def test_golden_fixtures(oracle):
         got = oracle.attention(q, k, v, float(data[f"{tag}_scale"]), causal)
         assert np.abs(got["o"] - data[f"{tag}_o"]).max() < 2e-5
         assert np.abs(got["lse"] - data[f"{tag}_lse"]).max() < 2e-5
+    data = np.load(os.path.join(GOLDEN, "attention_d128.npz"))
+    for tag in ("causal128", "offset128"):
+        q, k, v = data[f"{tag}_q"], data[f"{tag}_k"], data[f"{tag}_v"]
+        got = oracle.attention(q, k, v, float(data[f"{tag}_scale"]), bool(data[f"{tag}_causal"]))
+        assert np.abs(got["o"] - data[f"{tag}_o"]).max() < 2e-5
+        assert np.abs(got["lse"] - data[f"{tag}_lse"]).max() < 2e-5
     g = np.load(os.path.join(GOLDEN, "gemm_small.npz"))
     got = oracle.gemm(g["a"], g["b"], alpha=float(g["alpha"]), beta=float(g["beta"]), c_in=g["c_in"])
     assert np.abs(got - g["c"]).max() < 1e-4
