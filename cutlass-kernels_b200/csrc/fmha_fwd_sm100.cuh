@@ -312,6 +312,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         umma_commit_e<false>(bar_kv_empty + 0, leader);
       }
+      auto pv_qk_loop = [&](auto split_c) {     // two copies, as for the softmax warps
+      constexpr bool SPLIT = decltype(split_c)::value;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
@@ -335,7 +337,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const bool more = j + 1 < n_of(t);
           CFK_PROF_MARK(3)
           // with the two-term P the first-half barrier is not signalled; everything waits for the second
-          if (!split) {
+          if constexpr (!SPLIT) {
             ok = mbar_wait_warp(bar_p_full + 16 * t, j & 1, actx, kErrFmhaPFull);
             if (!ok) break;
             tc_fence_after_sync();
@@ -349,7 +351,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           CFK_PROF_MARK(2)
           if (!ok) break;
           tc_fence_after_sync();
-          if (split) {
+          if constexpr (SPLIT) {
             issue_pv_half(t, vslot, 0, j > 0 ? 1u : 0u);
             issue_pv_half(t, vslot, 1, 1u);
             issue_pv_lo(t, vslot);
@@ -367,6 +369,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit_e<false>(bar_kv_empty + 8 * vslot, leader);
           if (j + 1 < n_kv) umma_commit_e<false>(bar_kv_empty + 8 * kslot, leader);
         }
+      }
+      };
+      if constexpr (PT == kDtBF16) {
+        if (split) pv_qk_loop(std::true_type{});
+        else pv_qk_loop(std::false_type{});
+      } else {
+        pv_qk_loop(std::false_type{});
       }
       }
       CFK_PROF_MARK(3)
@@ -397,6 +406,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     [[maybe_unused]] uint32_t s_seen = 0u;
 
     CFK_PROF_DECL(8)
+    // The loop over the key tiles exists twice, with and without the two-term P: with both forms of the P store in one
+    // loop body every bf16 launch ran 4-7 % slower, also where no CTA used the second form.
+    auto key_tile_loop = [&](auto split_c) {
+    constexpr bool SPLIT = decltype(split_c)::value;
     for (int j = 0; j < n_my; ++j) {
       CFK_PROF_MARK(7)
       if (!(own_p && __all_sync(0xffffffffu, s_seen)))   // own_p: looked at while the previous tile's P was on its way
@@ -425,9 +438,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       {
         int lim = p.Skv - 1;
         if (p.causal) { const int cl = row_g + diag_off; lim = cl < lim ? cl : lim; }
-        ok = softmax_step<C, PT, HD, EMU>(sreg, tS, tP, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim, lim - j * C::BN,
-                                          split, bar_p_full + 16 * t, own_p ? bar_pv_done + 8 * t : 0u,
-                                          (uint32_t)(j - 1) & 1u, pv_seen, actx, m_ref, m_true, l);
+        ok = softmax_step<C, PT, HD, EMU, SPLIT>(sreg, tS, tP, tO, sl, j == 0, j * C::BN + 127 > tile_min_lim,
+                                                 lim - j * C::BN, bar_p_full + 16 * t, own_p ? bar_pv_done + 8 * t : 0u,
+                                                 (uint32_t)(j - 1) & 1u, pv_seen, actx, m_ref, m_true, l);
         if (!ok) break;
       }
       CFK_PROF_MARK(3)
@@ -437,6 +450,13 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before_sync();
       mbar_arrive_warp(bar_p_full + 16 * t + 8);
       CFK_PROF_MARK(4)
+    }
+    };
+    if constexpr (PT == kDtBF16) {
+      if (split) key_tile_loop(std::true_type{});
+      else key_tile_loop(std::false_type{});
+    } else {
+      key_tile_loop(std::false_type{});
     }
     CFK_PROF_MARK(7)
 

@@ -246,16 +246,16 @@ __device__ __forceinline__ void rescale_o_row(uint32_t tO, float alpha) {
 // of its own; tcgen05.st issued, not yet waited for) and m_ref / m_true / l are updated.  `first`: first
 // key tile of the row; `mask_tile`: this tile contains masked columns for some row, `lim` is this row's last visible
 // column.  `bar_half`: barrier that gets one arrival per warp once P of the first 64 keys is in tensor memory; not
-// used with the two-term P, whose second term goes to the upper half of S_t.
+// used with the two-term P (SPLIT, bf16 only), whose second term goes to the upper half of S_t.
 // When P has a buffer of its own (`bar_pv_done` != 0) the S buffer no longer says that P V of the previous key tile
 // has run (the next Q K^T was issued before it), so the thread waits for `bar_pv_done` before it touches O_t or the
 // P buffer again.  Returns false if
 // that wait gave up.  A look at a barrier costs one to several hundred clocks even when the barrier is complete
 // (the tensor core's operand reads keep the shared-memory port busy), so the caller looks early, with a test that
 // cannot put the warp to sleep, and hands the answer in.
-template <class CFG, int PT, int HD, int EMU>
+template <class CFG, int PT, int HD, int EMU, bool SPLIT>
 __device__ __forceinline__ bool softmax_step(uint32_t (&sreg)[128], uint32_t tS, uint32_t tP, uint32_t tO, float sl,
-                                             bool first, bool mask_tile, int lim, bool split, uint32_t bar_half,
+                                             bool first, bool mask_tile, int lim, uint32_t bar_half,
                                              uint32_t bar_pv_done, uint32_t pv_parity, uint32_t pv_seen,
                                              const AbortCtx& actx, float& m_ref, float& m_true, float& l) {
   // masking: columns beyond the causal limit of this row or beyond the key length.  Whether a tile
@@ -288,12 +288,8 @@ __device__ __forceinline__ bool softmax_step(uint32_t (&sreg)[128], uint32_t tS,
     }
   }
   const float negm = CFG::PSHIFT - m_ref * sl;
-  if constexpr (PT == kDtBF16) {
-    if (split) l += emit_p<128, PT, EMU, true>(sreg, tP, tS + 64, sl, negm);
-    else l += emit_p<128, PT, EMU, false, true>(sreg, tP, 0u, sl, negm, bar_half);
-  } else {
-    l += emit_p<128, PT, EMU, false, true>(sreg, tP, 0u, sl, negm, bar_half);
-  }
+  if constexpr (SPLIT) l += emit_p<128, PT, EMU, true>(sreg, tP, tS + 64, sl, negm);
+  else l += emit_p<128, PT, EMU, false, true>(sreg, tP, 0u, sl, negm, bar_half);
   return true;
 }
 
