@@ -161,7 +161,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (C::SEP_P) mode = kSepP;
     else if (p.sched == 1 && n_t0 > 0 && n_t1 > 0) mode = kSharedS;
   }
-  const bool qk_early = mode == kSepP;
   const uint32_t p_col0 = mode == kSepP ? C::P_COL0 : 128u;        // P_t at p_col0 + 64 t (kSepP, kSharedS)
 
   if (warp >= 8) {
@@ -312,8 +311,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         umma_commit_e<false>(bar_kv_empty + 0, leader);
       }
-      auto pv_qk_loop = [&](auto split_c) {     // two copies, as for the softmax warps
+      auto pv_qk_loop = [&](auto split_c, auto early_c) {     // one copy per case, as for the softmax warps
       constexpr bool SPLIT = decltype(split_c)::value;
+      constexpr bool qk_early = decltype(early_c)::value;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         const int vslot = vidx % C::NSLOT, kslot = kidx % C::NSLOT;
@@ -371,11 +371,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       };
-      if constexpr (PT == kDtBF16) {
-        if (split) pv_qk_loop(std::true_type{});
-        else pv_qk_loop(std::false_type{});
+      if (mode == kSepP) {
+        pv_qk_loop(std::false_type{}, std::true_type{});
       } else {
-        pv_qk_loop(std::false_type{});
+        if constexpr (PT == kDtBF16) {
+          if (split) pv_qk_loop(std::true_type{}, std::false_type{});
+          else pv_qk_loop(std::false_type{}, std::false_type{});
+        } else {
+          pv_qk_loop(std::false_type{}, std::false_type{});
+        }
       }
       }
       CFK_PROF_MARK(3)
@@ -388,9 +392,6 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int t = warp >> 2;               // query tile of this warpgroup
     const int r = tid & 127;               // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + (mode == kSharedS ? 0 : t * 128);
-    const uint32_t tP = mode == kOverS ? tS : tmem_base + lane_base + p_col0 + t * 64;
-    const bool own_p = mode != kOverS;     // P has a buffer of its own
     const uint32_t tO = tmem_base + lane_base + C::O_COL0 + t * HD;
     const int row_g = qblk * 256 + t * 128 + r;     // global query row
     const int n_my = n_of(t);
@@ -406,10 +407,15 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     [[maybe_unused]] uint32_t s_seen = 0u;
 
     CFK_PROF_DECL(8)
-    // The loop over the key tiles exists twice, with and without the two-term P: with both forms of the P store in one
-    // loop body every bf16 launch ran 4-7 % slower, also where no CTA used the second form.
-    auto key_tile_loop = [&](auto split_c) {
+    // The loop over the key tiles exists once per form of the P store (two-term or plain) and per schedule: with both
+    // forms of the store in one loop body every bf16 launch ran 4-7 % slower, also where no CTA used the second form,
+    // and the schedule as a run-time value cost the 16-bit shapes at d = 128 another 2 %.
+    auto key_tile_loop = [&](auto split_c, auto mode_c) {
     constexpr bool SPLIT = decltype(split_c)::value;
+    constexpr int MODE = decltype(mode_c)::value;
+    constexpr bool own_p = MODE != kOverS;     // P has a buffer of its own
+    const uint32_t tS = tmem_base + lane_base + (MODE == kSharedS ? 0 : t * 128);
+    const uint32_t tP = MODE == kOverS ? tS : tmem_base + lane_base + (MODE == kSepP ? C::P_COL0 : 128) + t * 64;
     for (int j = 0; j < n_my; ++j) {
       CFK_PROF_MARK(7)
       if (!(own_p && __all_sync(0xffffffffu, s_seen)))   // own_p: looked at while the previous tile's P was on its way
@@ -427,7 +433,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       uint32_t pv_seen = 0u;
       if (own_p && j > 0) pv_seen = mbar_test_wait(bar_pv_done + 8 * t, (uint32_t)(j - 1) & 1u);
       tmem_wait_ld();
-      if (mode == kSharedS) {   // the S buffer may take the other tile's scores
+      if constexpr (MODE == kSharedS) {   // the S buffer may take the other tile's scores
         tc_fence_before_sync();
         mbar_arrive_warp(bar_s_read + 8 * t);
       }
@@ -452,11 +458,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       CFK_PROF_MARK(4)
     }
     };
-    if constexpr (PT == kDtBF16) {
-      if (split) key_tile_loop(std::true_type{});
-      else key_tile_loop(std::false_type{});
+    using OverS = std::integral_constant<int, kOverS>;
+    using OwnP = std::integral_constant<int, C::SEP_P ? kSepP : kSharedS>;
+    if (mode != kOverS) {
+      key_tile_loop(std::false_type{}, OwnP{});
     } else {
-      key_tile_loop(std::false_type{});
+      if constexpr (PT == kDtBF16) {
+        if (split) key_tile_loop(std::true_type{}, OverS{});
+        else key_tile_loop(std::false_type{}, OverS{});
+      } else {
+        key_tile_loop(std::false_type{}, OverS{});
+      }
     }
     CFK_PROF_MARK(7)
 
