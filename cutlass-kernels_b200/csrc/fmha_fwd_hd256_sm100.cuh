@@ -251,6 +251,10 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     bool ok = true;
     uint32_t sreg[128];
 
+    // One copy of the loop per form of the P store (two-term or plain): with both forms in one loop body a bf16
+    // launch runs slower also where no CTA uses the second form.
+    auto key_tile_loop = [&](auto split_c) {
+    constexpr bool SPLIT = decltype(split_c)::value;
     for (int j = 0; j < n_kv; ++j) {
       const int x = j & 1;
       const uint32_t tS = tmem_base + lane_base + x * 128;
@@ -293,15 +297,17 @@ fmha_fwd_hd256_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       }
       const float negm = C::PSHIFT - m_ref * sl;
-      if constexpr (PT == kDtBF16) {
-        if (split) l += emit_p128<PT, EMU, true>(sreg, tS, tS + 64, sl, negm);
-        else l += emit_p128<PT, EMU, false>(sreg, tS, tS + 64, sl, negm);
-      } else {
-        l += emit_p128<PT, EMU, false>(sreg, tS, tS + 64, sl, negm);
-      }
+      l += emit_p128<PT, EMU, SPLIT>(sreg, tS, tS + 64, sl, negm);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive_warp(bar_p_full + 8 * x);
+    }
+    };
+    if constexpr (PT == kDtBF16) {
+      if (split) key_tile_loop(std::true_type{});
+      else key_tile_loop(std::false_type{});
+    } else {
+      key_tile_loop(std::false_type{});
     }
 
     if (ok && n_kv > 0) {
